@@ -1,0 +1,713 @@
+// libfp8bs.so: the C ABI declared in include/fp8bs.h -- argument checking, run-time shape
+// dispatch, TMA descriptor construction and kernel launches.  Host-side role of the
+// reference's gemmGPU wrapper and its geometry switch (check.cu:51-130).
+#include "../../include/fp8bs.h"
+#include "gemm_kernel.cuh"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+
+#include <atomic>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <new>
+
+namespace fp8bs {
+
+// ---------------------------------------------------------------------------------------
+// per-thread / per-process state
+// ---------------------------------------------------------------------------------------
+static thread_local int tl_last_cuda_error = 0;
+static std::atomic<unsigned long long> g_launches{0};
+
+// Device status word written by kernels whose bounded waits expire.
+__device__ unsigned int g_device_status[4];
+
+#define CUDA_TRY(expr)                                     \
+    do {                                                   \
+        cudaError_t e__ = (expr);                          \
+        if (e__ != cudaSuccess) {                          \
+            tl_last_cuda_error = static_cast<int>(e__);    \
+            (void)cudaGetLastError();                      \
+            return FP8BS_ERR_CUDA;                         \
+        }                                                  \
+    } while (0)
+
+constexpr int MAX_DEVICES = 64;
+constexpr size_t COUNTER_BYTES = 65536;            // head of the workspace: 16384 tile counters
+constexpr int MAX_SPLITS = 32;
+
+struct DeviceInfo {
+    bool ready = false;
+    int status = FP8BS_OK;
+    int sm_count = 0;
+    unsigned int* status_ptr = nullptr;            // device address of g_device_status
+};
+static DeviceInfo g_dev[MAX_DEVICES];
+static std::mutex g_dev_mutex;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+static EncodeTiledFn g_encode_tiled = nullptr;
+
+template <int BN, bool SPLITK>
+static int prepare_kernel()
+{
+    CUDA_TRY(cudaFuncSetAttribute(gemm_kernel<BN, SPLITK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  TileCfg<BN>::SMEM_BYTES));
+    return FP8BS_OK;
+}
+
+// One-time set-up for the current device: capability check, kernel attributes, driver
+// entry point for tensor-map encoding (looked up at run time so that the library has no
+// link-time dependency on libcuda and loads on a machine without a driver).
+static int device_setup(DeviceInfo** out)
+{
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) {
+        (void)cudaGetLastError();
+        return FP8BS_ERR_NO_DEVICE;
+    }
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
+    DeviceInfo& d = g_dev[dev];
+    if (!d.ready) {
+        d.ready = true;
+        d.status = FP8BS_ERR_NO_DEVICE;
+        int major = 0;
+        if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess || major != 10) {
+            (void)cudaGetLastError();
+            return d.status;
+        }
+        if (cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return d.status;
+        if (!g_encode_tiled) {
+            void* fn = nullptr;
+            cudaDriverEntryPointQueryResult qres;
+            if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+                qres != cudaDriverEntryPointSuccess || !fn) {
+                (void)cudaGetLastError();
+                return d.status;
+            }
+            g_encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
+        }
+        int rc;
+        if ((rc = prepare_kernel<128, false>()) || (rc = prepare_kernel<256, false>()) ||
+            (rc = prepare_kernel<128, true>()) || (rc = prepare_kernel<256, true>())) {
+            d.status = rc;
+            return rc;
+        }
+        void* sp = nullptr;
+        if (cudaGetSymbolAddress(&sp, g_device_status) != cudaSuccess) {
+            (void)cudaGetLastError();
+            d.status = FP8BS_ERR_CUDA;
+            return d.status;
+        }
+        d.status_ptr = static_cast<unsigned int*>(sp);
+        if (cudaMemset(sp, 0, sizeof(unsigned int) * 4) != cudaSuccess) {
+            (void)cudaGetLastError();
+            d.status = FP8BS_ERR_CUDA;
+            return d.status;
+        }
+        d.status = FP8BS_OK;
+    }
+    if (out) *out = &d;
+    return d.status;
+}
+
+// ---------------------------------------------------------------------------------------
+// dispatch
+// ---------------------------------------------------------------------------------------
+struct Config {
+    int path;     // FP8BS_PATH_MN_LARGE / FP8BS_PATH_MN_SMALL
+    int tile_n;   // 128 or 256
+    int splits;   // 1 for mn_large
+};
+
+static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+constexpr int SM_TARGET = 148;   // B200; the dispatch is a pure function of the shape
+
+// Estimated cost of a configuration in units of "one 128x128x128 block on one SM".
+static double config_cost(int M, int N, int K, int tile_n, int splits)
+{
+    const int KB = K / 128;
+    const int tiles = ceil_div(M, 128) * ceil_div(N, tile_n);
+    const int units = tiles * splits;
+    const int waves = ceil_div(units, SM_TARGET);
+    const double per_kb = (tile_n == 256) ? 2.0 : 1.2;       // a 128-wide tile re-reads A twice as often
+    const double per_unit = ceil_div(KB, splits) * per_kb + 4.0 * (tile_n / 128);   // + prologue/epilogue
+    double cost = waves * per_unit;
+    if (splits > 1) cost += 3.0 + 0.75 * splits;             // partial-sum round trip through L2
+    return cost;
+}
+
+static Config choose_config(int M, int N, int K, int path, int splits, int tile_n)
+{
+    const int KB = K / 128;
+    Config best{FP8BS_PATH_MN_LARGE, 128, 1};
+    double best_cost = 1e300;
+    for (int tn = 128; tn <= 256; tn += 128) {
+        if (tile_n && tile_n != tn) continue;
+        const int smax = (path == FP8BS_PATH_MN_LARGE) ? 1 : (KB < MAX_SPLITS ? KB : MAX_SPLITS);
+        for (int s = 1; s <= smax; ++s) {
+            if (splits && s != splits) continue;
+            const double c = config_cost(M, N, K, tn, s);
+            if (c < best_cost) {
+                best_cost = c;
+                best = Config{(s > 1 || path == FP8BS_PATH_MN_SMALL) ? FP8BS_PATH_MN_SMALL : FP8BS_PATH_MN_LARGE, tn, s};
+            }
+        }
+    }
+    return best;
+}
+
+static size_t config_workspace(int M, int N, const Config& c)
+{
+    if (c.path != FP8BS_PATH_MN_SMALL) return 0;
+    const size_t tiles = static_cast<size_t>(ceil_div(M, 128)) * ceil_div(N, c.tile_n);
+    return COUNTER_BYTES + tiles * c.splits * (static_cast<size_t>(c.tile_n) * 128 * sizeof(float));
+}
+
+static int check_shape(int M, int N, int K)
+{
+    if (M <= 0 || N <= 0 || K <= 0 || K % 128 != 0) return FP8BS_ERR_SHAPE;
+    if (M % 16 != 0 || N % 16 != 0) return FP8BS_ERR_ALIGN;
+    return FP8BS_OK;
+}
+
+static int check_args(int M, int N, int K, int n0, int n_total, int path, int splits, int tile_n)
+{
+    int rc = check_shape(M, N, K);
+    if (rc) return rc;
+    if (path < FP8BS_PATH_AUTO || path > FP8BS_PATH_MN_SMALL) return FP8BS_ERR_ARG;
+    if (splits < 0 || splits > K / 128 || splits > MAX_SPLITS) return FP8BS_ERR_ARG;
+    if (path == FP8BS_PATH_MN_LARGE && splits > 1) return FP8BS_ERR_ARG;
+    if (tile_n != 0 && tile_n != 128 && tile_n != 256) return FP8BS_ERR_ARG;
+    if (n0 < 0 || n0 % 64 != 0 || n_total < n0 + N) return FP8BS_ERR_ARG;
+    return FP8BS_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// launch
+// ---------------------------------------------------------------------------------------
+static int encode_operand_map(CUtensorMap* tm, const void* base, int mn, int K)
+{
+    // Global view: 8-bit elements, dimension 0 = M (or N), contiguous; dimension 1 = K with
+    // a stride of M (or N) bytes.  Box = 128 x 128, 128-byte swizzle, zero fill outside.
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(mn), static_cast<cuuint64_t>(K)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(mn)};
+    const cuuint32_t box[2] = {128u, 128u};
+    const cuuint32_t estr[2] = {1u, 1u};
+    const CUresult r = g_encode_tiled(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides,
+                                      box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        tl_last_cuda_error = static_cast<int>(r);
+        return FP8BS_ERR_CUDA;
+    }
+    return FP8BS_OK;
+}
+
+template <int BN, bool SPLITK>
+static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int sm_count,
+                  cudaStream_t stream)
+{
+    const int units = p.m_tiles * p.n_tiles * p.splits;
+    const int grid = units < sm_count ? units : sm_count;
+    gemm_kernel<BN, SPLITK><<<grid, TileCfg<BN>::THREADS, TileCfg<BN>::SMEM_BYTES, stream>>>(tmA, tmB, p);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    CUDA_TRY(cudaGetLastError());
+    return FP8BS_OK;
+}
+
+static int gemm_impl(const void* A, const void* B, const float* a_scale, const float* b_scale, void* C, int M,
+                     int N, int K, int n0, int n_total, int path, int splits, int tile_n, void* workspace,
+                     size_t workspace_bytes, void* stream)
+{
+    if (!A || !B || !a_scale || !b_scale || !C) return FP8BS_ERR_NULL;
+    int rc = check_args(M, N, K, n0, n_total, path, splits, tile_n);
+    if (rc) return rc;
+    if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15u)
+        return FP8BS_ERR_ALIGN;
+    if ((reinterpret_cast<uintptr_t>(a_scale) | reinterpret_cast<uintptr_t>(b_scale)) & 3u) return FP8BS_ERR_ALIGN;
+
+    Config cfg = choose_config(M, N, K, path, splits, tile_n);
+    if (cfg.path == FP8BS_PATH_MN_SMALL) {
+        const size_t need = config_workspace(M, N, cfg);
+        const size_t tiles = static_cast<size_t>(ceil_div(M, 128)) * ceil_div(N, cfg.tile_n);
+        const bool fits = workspace && workspace_bytes >= need && tiles <= COUNTER_BYTES / sizeof(unsigned int) &&
+                          (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0;
+        if (!fits) {
+            if (path != FP8BS_PATH_AUTO) return FP8BS_ERR_WORKSPACE;
+            cfg = choose_config(M, N, K, FP8BS_PATH_MN_LARGE, 1, tile_n);   // best full-K configuration
+        }
+    }
+
+    DeviceInfo* dev = nullptr;
+    rc = device_setup(&dev);
+    if (rc) return rc;
+
+    CUtensorMap tmA, tmB;
+    if ((rc = encode_operand_map(&tmA, A, M, K))) return rc;
+    if ((rc = encode_operand_map(&tmB, B, N, K))) return rc;
+
+    GemmParams p;
+    p.a_scale = a_scale;
+    p.b_scale = b_scale;
+    p.C = static_cast<__nv_bfloat16*>(C);
+    p.partials = nullptr;
+    p.counters = nullptr;
+    p.status = dev->status_ptr;
+    p.M = M; p.N = N; p.K = K;
+    p.n_off = n0;
+    p.sn = ceil_div(n_total, 128);
+    p.m_tiles = ceil_div(M, 128);
+    p.n_tiles = ceil_div(N, cfg.tile_n);
+    p.splits = cfg.splits;
+    p.elem_scale = 1.0f;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+    if (cfg.path == FP8BS_PATH_MN_SMALL) {
+        p.counters = static_cast<unsigned int*>(workspace);
+        p.partials = reinterpret_cast<float4*>(static_cast<char*>(workspace) + COUNTER_BYTES);
+        return cfg.tile_n == 256 ? launch<256, true>(tmA, tmB, p, dev->sm_count, st)
+                                 : launch<128, true>(tmA, tmB, p, dev->sm_count, st);
+    }
+    return cfg.tile_n == 256 ? launch<256, false>(tmA, tmB, p, dev->sm_count, st)
+                             : launch<128, false>(tmA, tmB, p, dev->sm_count, st);
+}
+
+// ---------------------------------------------------------------------------------------
+// scalar kernels: ground truth restated (check.cu:30-49) and fp32 -> fp8 (check.cu:17-22)
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ float e4m3fn_decode(uint8_t b)
+{
+    const uint32_t e = (b >> 3) & 0xFu, m = b & 7u;
+    float v;
+    if (e == 0xFu && m == 7u) v = __int_as_float(0x7fc00000);
+    else if (e == 0u) v = static_cast<float>(m) * 0.001953125f;                    // m * 2^-9
+    else v = __int_as_float(((e + 120u) << 23) | (m << 20));                         // (1 + m/8) * 2^(e-7)
+    return (b & 0x80u) ? -v : v;
+}
+
+// Thread (n, m): n across the warp so the B reads coalesce; per 128-K block a sequential
+// fp32 sum, then result += block * as * bs, then a round-to-nearest-even bf16 cast.
+__global__ void ref_gemm_kernel(const uint8_t* __restrict__ A, const uint8_t* __restrict__ B,
+                                const float* __restrict__ as, const float* __restrict__ bs,
+                                __nv_bfloat16* __restrict__ C, int M, int N, int K)
+{
+    const int n = blockIdx.x * blockDim.x + threadIdx.x;
+    const int m = blockIdx.y * blockDim.y + threadIdx.y;
+    if (m >= M || n >= N) return;
+    const int sn = (N + 127) / 128;
+    float result = 0.0f;
+    for (int kb = 0; kb < K / 128; ++kb) {
+        float block = 0.0f;
+        for (int kk = 0; kk < 128; ++kk) {
+            const size_t k = static_cast<size_t>(kb) * 128 + kk;
+            block = __fmaf_rn(e4m3fn_decode(A[m + k * M]), e4m3fn_decode(B[n + k * N]), block);
+        }
+        result = __fadd_rn(result, __fmul_rn(__fmul_rn(block, as[m + static_cast<size_t>(kb) * M]),
+                                             bs[n / 128 + static_cast<size_t>(kb) * sn]));
+    }
+    C[static_cast<size_t>(m) * N + n] = __float2bfloat16_rn(result);
+}
+
+__host__ __device__ inline uint8_t float_to_e4m3fn_rne(float x)
+{
+    uint32_t u;
+#ifdef __CUDA_ARCH__
+    u = __float_as_uint(x);
+#else
+    std::memcpy(&u, &x, 4);
+#endif
+    const uint8_t sign = static_cast<uint8_t>((u >> 24) & 0x80u);
+    const uint32_t a = u & 0x7fffffffu;
+    if (a > 0x7f800000u) return 0x7F;                         // NaN
+    if (a >= 0x43e80000u) return sign | 0x7E;                 // >= 464 (and inf): saturate to 448
+    if (a < 0x3a800000u) {                                    // < 2^-10: rounds to 0 or the first subnormal
+        // 2^-10 itself is the midpoint between 0 and 2^-9 and ties to even (0)
+        return sign;
+    }
+    const int e = static_cast<int>(a >> 23) - 127;            // unbiased exponent
+    if (e < -6) {
+        // subnormal target: value = q * 2^-9, q in 0..8 (8 promotes to the first normal)
+        const uint32_t mant = (a & 0x7fffffu) | 0x800000u;    // 1.m as a 24-bit integer, value mant * 2^(e-23)
+        const int shift = (-9) - (e - 23);                    // q = mant >> shift, shift = 14 - e in 21..24
+        uint32_t q = mant >> shift;
+        const uint32_t rem = mant & ((1u << shift) - 1u), half = 1u << (shift - 1);
+        if (rem > half || (rem == half && (q & 1u))) ++q;
+        return sign | static_cast<uint8_t>(q);                // q == 8 is exactly the encoding of 2^-6
+    }
+    uint32_t q = (a >> 20) & 7u;                              // top three mantissa bits
+    const uint32_t rem = a & 0xfffffu, half = 0x80000u;
+    uint32_t be = static_cast<uint32_t>(e + 7);
+    if (rem > half || (rem == half && (q & 1u))) {
+        if (++q == 8u) { q = 0u; ++be; }
+    }
+    if (be > 15u || (be == 15u && q == 7u)) return sign | 0x7E;
+    return sign | static_cast<uint8_t>((be << 3) | q);
+}
+
+__global__ void convert_float_to_e4m3fn_kernel(const float* __restrict__ in, uint8_t* __restrict__ out, size_t n)
+{
+    const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = float_to_e4m3fn_rne(in[i]);
+}
+
+// ---------------------------------------------------------------------------------------
+// host generator helpers
+// ---------------------------------------------------------------------------------------
+static inline uint64_t mix64(uint64_t z)
+{
+    z += 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+static inline float u01(uint64_t bits) { return static_cast<float>((bits >> 40) + 1) * (1.0f / 16777217.0f); }  // (0,1)
+
+static float host_e4m3fn_to_float(uint8_t b)
+{
+    const int e = (b >> 3) & 0xF, m = b & 7;
+    float v;
+    if (e == 0xF && m == 7) return NAN;
+    if (e == 0) v = std::ldexp(static_cast<float>(m), -9);
+    else v = std::ldexp(static_cast<float>(8 + m), e - 10);
+    return (b & 0x80) ? -v : v;
+}
+
+struct fp8bs_host_ctx_impl {
+    size_t max_M, max_N, max_K;
+    void *dA, *dB, *dAs, *dBs, *dC, *dW;
+    void *hA, *hB, *hAs, *hBs, *hC;
+    size_t w_bytes;
+    cudaStream_t stream;
+};
+
+}  // namespace fp8bs
+
+using namespace fp8bs;
+
+// =======================================================================================
+// exported C ABI
+// =======================================================================================
+extern "C" {
+
+int fp8bs_gemm(const void* A, const void* B, const float* a_scale, const float* b_scale, void* C, int M, int N,
+               int K, void* workspace, size_t workspace_bytes, void* stream)
+{
+    return gemm_impl(A, B, a_scale, b_scale, C, M, N, K, 0, N, FP8BS_PATH_AUTO, 0, 0, workspace, workspace_bytes,
+                     stream);
+}
+
+int fp8bs_gemm_mn_large(const void* A, const void* B, const float* a_scale, const float* b_scale, void* C, int M,
+                        int N, int K, void* stream)
+{
+    return gemm_impl(A, B, a_scale, b_scale, C, M, N, K, 0, N, FP8BS_PATH_MN_LARGE, 1, 0, nullptr, 0, stream);
+}
+
+int fp8bs_gemm_mn_small(const void* A, const void* B, const float* a_scale, const float* b_scale, void* C, int M,
+                        int N, int K, int splits, void* workspace, size_t workspace_bytes, void* stream)
+{
+    return gemm_impl(A, B, a_scale, b_scale, C, M, N, K, 0, N, FP8BS_PATH_MN_SMALL, splits, 0, workspace,
+                     workspace_bytes, stream);
+}
+
+int fp8bs_gemm_ex(const void* A, const void* B, const float* a_scale, const float* b_scale, void* C, int M, int N,
+                  int K, int n0, int n_total, int path, int splits, int tile_n, void* workspace,
+                  size_t workspace_bytes, void* stream)
+{
+    return gemm_impl(A, B, a_scale, b_scale, C, M, N, K, n0, n_total, path, splits, tile_n, workspace,
+                     workspace_bytes, stream);
+}
+
+int fp8bs_gemm_ref(const void* A, const void* B, const float* a_scale, const float* b_scale, void* C, int M, int N,
+                   int K, void* stream)
+{
+    if (!A || !B || !a_scale || !b_scale || !C) return FP8BS_ERR_NULL;
+    if (M <= 0 || N <= 0 || K <= 0 || K % 128 != 0) return FP8BS_ERR_SHAPE;
+    const dim3 block(32, 8), grid(ceil_div(N, 32), ceil_div(M, 8));
+    ref_gemm_kernel<<<grid, block, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint8_t*>(A), static_cast<const uint8_t*>(B), a_scale, b_scale,
+        static_cast<__nv_bfloat16*>(C), M, N, K);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    CUDA_TRY(cudaGetLastError());
+    return FP8BS_OK;
+}
+
+int fp8bs_select_path(int M, int N, int K, int* splits, int* tile_n)
+{
+    const int rc = check_shape(M, N, K);
+    if (rc) return rc;
+    const Config c = choose_config(M, N, K, FP8BS_PATH_AUTO, 0, 0);
+    if (splits) *splits = c.splits;
+    if (tile_n) *tile_n = c.tile_n;
+    return c.path;
+}
+
+size_t fp8bs_workspace_bytes(int M, int N, int K)
+{
+    if (check_shape(M, N, K)) return 0;
+    return config_workspace(M, N, choose_config(M, N, K, FP8BS_PATH_AUTO, 0, 0));
+}
+
+size_t fp8bs_workspace_bytes_ex(int M, int N, int K, int path, int splits, int tile_n)
+{
+    if (check_args(M, N, K, 0, N, path, splits, tile_n)) return 0;
+    return config_workspace(M, N, choose_config(M, N, K, path, splits, tile_n));
+}
+
+int fp8bs_workspace_init(void* workspace, size_t workspace_bytes, void* stream)
+{
+    if (!workspace) return FP8BS_ERR_NULL;
+    if (workspace_bytes < COUNTER_BYTES) return FP8BS_ERR_WORKSPACE;
+    CUDA_TRY(cudaMemsetAsync(workspace, 0, COUNTER_BYTES, static_cast<cudaStream_t>(stream)));
+    return FP8BS_OK;
+}
+
+int fp8bs_last_device_status(void* stream, unsigned int* detail)
+{
+    DeviceInfo* dev = nullptr;
+    const int rc = device_setup(&dev);
+    if (rc) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    CUDA_TRY(cudaStreamSynchronize(st));
+    unsigned int word = 0;
+    CUDA_TRY(cudaMemcpy(&word, dev->status_ptr, sizeof(word), cudaMemcpyDeviceToHost));
+    if (detail) *detail = word;
+    if (word != 0) {
+        CUDA_TRY(cudaMemset(dev->status_ptr, 0, sizeof(word)));
+        return FP8BS_ERR_DEVICE_TIMEOUT;
+    }
+    return FP8BS_OK;
+}
+
+const char* fp8bs_status_string(int status)
+{
+    switch (status) {
+        case FP8BS_OK: return "ok";
+        case FP8BS_ERR_NULL: return "a required pointer is NULL";
+        case FP8BS_ERR_SHAPE: return "bad shape: M, N, K must be positive and K a multiple of 128";
+        case FP8BS_ERR_ALIGN: return "alignment: M and N must be multiples of 16; A, B, C 16-byte aligned";
+        case FP8BS_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
+        case FP8BS_ERR_ARG: return "bad path, splits, tile_n, n0 or n_total argument";
+        case FP8BS_ERR_NO_DEVICE: return "no usable sm_100 device (this library has no CPU fallback)";
+        case FP8BS_ERR_CUDA: return "a CUDA call failed (see fp8bs_last_cuda_error)";
+        case FP8BS_ERR_DEVICE_TIMEOUT: return "a kernel gave up waiting on a barrier";
+        case FP8BS_ERR_FP8_BYTE: return "fp8 byte has no equal value in the other dialect";
+        default: return "unknown status";
+    }
+}
+
+int fp8bs_last_cuda_error(void) { return tl_last_cuda_error; }
+unsigned long long fp8bs_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+// ---- gemmGPU mirror -------------------------------------------------------------------
+int fp8bs_gemmGPU(uint16_t* C, const float* A, const float* B, const float* a_scale, const float* b_scale, size_t M,
+                  size_t N, size_t K, int option)
+{
+    if (!C || !A || !B || !a_scale || !b_scale) return FP8BS_ERR_NULL;
+    if (option < 0 || option > 2) return FP8BS_ERR_ARG;
+    if (M > 0x7fffffff || N > 0x7fffffff || K > 0x7fffffff) return FP8BS_ERR_SHAPE;
+    int rc = check_shape(static_cast<int>(M), static_cast<int>(N), static_cast<int>(K));
+    if (rc) return rc;
+    const size_t sn = (N + 127) / 128, KB = K / 128;
+    float *dA = nullptr, *dB = nullptr, *dAs = nullptr, *dBs = nullptr;
+    uint8_t *dA8 = nullptr, *dB8 = nullptr;
+    void *dC = nullptr, *dW = nullptr;
+    size_t wbytes = 0;
+    auto cleanup = [&]() {
+        cudaFree(dA); cudaFree(dB); cudaFree(dAs); cudaFree(dBs); cudaFree(dA8); cudaFree(dB8); cudaFree(dC); cudaFree(dW);
+    };
+#define GG_TRY(expr)                                                        \
+    do {                                                                    \
+        cudaError_t e__ = (expr);                                           \
+        if (e__ != cudaSuccess) {                                           \
+            tl_last_cuda_error = static_cast<int>(e__);                     \
+            (void)cudaGetLastError();                                       \
+            cleanup();                                                      \
+            return FP8BS_ERR_CUDA;                                          \
+        }                                                                   \
+    } while (0)
+    GG_TRY(cudaMalloc(&dA, sizeof(float) * M * K));
+    GG_TRY(cudaMalloc(&dB, sizeof(float) * N * K));
+    GG_TRY(cudaMalloc(&dC, sizeof(uint16_t) * M * N));
+    GG_TRY(cudaMalloc(&dAs, sizeof(float) * M * KB));
+    GG_TRY(cudaMalloc(&dBs, sizeof(float) * sn * KB));
+    GG_TRY(cudaMemcpy(dA, A, sizeof(float) * M * K, cudaMemcpyHostToDevice));
+    GG_TRY(cudaMemcpy(dB, B, sizeof(float) * N * K, cudaMemcpyHostToDevice));
+    GG_TRY(cudaMemcpy(dAs, a_scale, sizeof(float) * M * KB, cudaMemcpyHostToDevice));
+    GG_TRY(cudaMemcpy(dBs, b_scale, sizeof(float) * sn * KB, cudaMemcpyHostToDevice));
+    GG_TRY(cudaMalloc(&dA8, M * K));
+    GG_TRY(cudaMalloc(&dB8, N * K));
+    convert_float_to_e4m3fn_kernel<<<static_cast<unsigned>((M * K + 255) / 256), 256>>>(dA, dA8, M * K);
+    convert_float_to_e4m3fn_kernel<<<static_cast<unsigned>((N * K + 255) / 256), 256>>>(dB, dB8, N * K);
+    g_launches.fetch_add(2, std::memory_order_relaxed);
+    GG_TRY(cudaGetLastError());
+    const int m = static_cast<int>(M), n = static_cast<int>(N), k = static_cast<int>(K);
+    if (option == 2) {
+        rc = fp8bs_gemm_ref(dA8, dB8, dAs, dBs, dC, m, n, k, nullptr);
+    } else {
+        const int path = option == 1 ? FP8BS_PATH_MN_SMALL : FP8BS_PATH_AUTO;
+        wbytes = fp8bs_workspace_bytes_ex(m, n, k, path, 0, 0);
+        if (wbytes) {
+            GG_TRY(cudaMalloc(&dW, wbytes));
+            GG_TRY(cudaMemset(dW, 0, COUNTER_BYTES));
+        }
+        rc = gemm_impl(dA8, dB8, dAs, dBs, dC, m, n, k, 0, n, path, 0, 0, dW, wbytes, nullptr);
+    }
+    if (rc == FP8BS_OK) {
+        GG_TRY(cudaMemcpy(C, dC, sizeof(uint16_t) * M * N, cudaMemcpyDeviceToHost));
+        rc = fp8bs_last_device_status(nullptr, nullptr);
+    }
+    cleanup();
+#undef GG_TRY
+    return rc;
+}
+
+// ---- reusable end-to-end context ------------------------------------------------------
+int fp8bs_host_ctx_create(fp8bs_host_ctx** out, size_t max_M, size_t max_N, size_t max_K)
+{
+    if (!out) return FP8BS_ERR_NULL;
+    *out = nullptr;
+    if (max_M == 0 || max_N == 0 || max_K == 0 || max_K % 128 != 0) return FP8BS_ERR_SHAPE;
+    DeviceInfo* dev = nullptr;
+    int rc = device_setup(&dev);
+    if (rc) return rc;
+    fp8bs_host_ctx_impl* c = new (std::nothrow) fp8bs_host_ctx_impl();
+    if (!c) return FP8BS_ERR_CUDA;
+    std::memset(c, 0, sizeof(*c));
+    c->max_M = max_M; c->max_N = max_N; c->max_K = max_K;
+    const size_t KB = max_K / 128, sn = (max_N + 127) / 128;
+    // split-K is only ever chosen for small M*N; 64 MiB covers every such configuration
+    c->w_bytes = static_cast<size_t>(64) << 20;
+    bool ok = cudaMalloc(&c->dA, max_M * max_K) == cudaSuccess && cudaMalloc(&c->dB, max_N * max_K) == cudaSuccess &&
+              cudaMalloc(&c->dAs, max_M * KB * 4) == cudaSuccess && cudaMalloc(&c->dBs, sn * KB * 4) == cudaSuccess &&
+              cudaMalloc(&c->dC, max_M * max_N * 2) == cudaSuccess && cudaMalloc(&c->dW, c->w_bytes) == cudaSuccess &&
+              cudaMallocHost(&c->hA, max_M * max_K) == cudaSuccess && cudaMallocHost(&c->hB, max_N * max_K) == cudaSuccess &&
+              cudaMallocHost(&c->hAs, max_M * KB * 4) == cudaSuccess && cudaMallocHost(&c->hBs, sn * KB * 4) == cudaSuccess &&
+              cudaMallocHost(&c->hC, max_M * max_N * 2) == cudaSuccess &&
+              cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) == cudaSuccess &&
+              cudaMemset(c->dW, 0, COUNTER_BYTES) == cudaSuccess;
+    if (!ok) {
+        tl_last_cuda_error = static_cast<int>(cudaGetLastError());
+        fp8bs_host_ctx_destroy(reinterpret_cast<fp8bs_host_ctx*>(c));
+        return FP8BS_ERR_CUDA;
+    }
+    *out = reinterpret_cast<fp8bs_host_ctx*>(c);
+    return FP8BS_OK;
+}
+
+int fp8bs_host_ctx_destroy(fp8bs_host_ctx* ctx)
+{
+    if (!ctx) return FP8BS_OK;
+    fp8bs_host_ctx_impl* c = reinterpret_cast<fp8bs_host_ctx_impl*>(ctx);
+    if (c->stream) cudaStreamDestroy(c->stream);
+    cudaFree(c->dA); cudaFree(c->dB); cudaFree(c->dAs); cudaFree(c->dBs); cudaFree(c->dC); cudaFree(c->dW);
+    cudaFreeHost(c->hA); cudaFreeHost(c->hB); cudaFreeHost(c->hAs); cudaFreeHost(c->hBs); cudaFreeHost(c->hC);
+    (void)cudaGetLastError();
+    delete c;
+    return FP8BS_OK;
+}
+
+void* fp8bs_host_ctx_buffer(fp8bs_host_ctx* ctx, int which)
+{
+    if (!ctx) return nullptr;
+    fp8bs_host_ctx_impl* c = reinterpret_cast<fp8bs_host_ctx_impl*>(ctx);
+    switch (which) {
+        case 0: return c->hA;
+        case 1: return c->hB;
+        case 2: return c->hAs;
+        case 3: return c->hBs;
+        case 4: return c->hC;
+        default: return nullptr;
+    }
+}
+
+int fp8bs_gemm_host(fp8bs_host_ctx* ctx, uint16_t* C, const void* A, const void* B, const float* a_scale,
+                    const float* b_scale, int M, int N, int K)
+{
+    if (!ctx || !C || !A || !B || !a_scale || !b_scale) return FP8BS_ERR_NULL;
+    fp8bs_host_ctx_impl* c = reinterpret_cast<fp8bs_host_ctx_impl*>(ctx);
+    int rc = check_shape(M, N, K);
+    if (rc) return rc;
+    if (static_cast<size_t>(M) > c->max_M || static_cast<size_t>(N) > c->max_N || static_cast<size_t>(K) > c->max_K)
+        return FP8BS_ERR_SHAPE;
+    const size_t KB = K / 128, sn = (N + 127) / 128;
+    CUDA_TRY(cudaMemcpyAsync(c->dA, A, static_cast<size_t>(M) * K, cudaMemcpyHostToDevice, c->stream));
+    CUDA_TRY(cudaMemcpyAsync(c->dB, B, static_cast<size_t>(N) * K, cudaMemcpyHostToDevice, c->stream));
+    CUDA_TRY(cudaMemcpyAsync(c->dAs, a_scale, static_cast<size_t>(M) * KB * 4, cudaMemcpyHostToDevice, c->stream));
+    CUDA_TRY(cudaMemcpyAsync(c->dBs, b_scale, sn * KB * 4, cudaMemcpyHostToDevice, c->stream));
+    rc = gemm_impl(c->dA, c->dB, static_cast<const float*>(c->dAs), static_cast<const float*>(c->dBs), c->dC, M, N, K,
+                   0, N, FP8BS_PATH_AUTO, 0, 0, c->dW, c->w_bytes, c->stream);
+    if (rc) return rc;
+    CUDA_TRY(cudaMemcpyAsync(C, c->dC, static_cast<size_t>(M) * N * 2, cudaMemcpyDeviceToHost, c->stream));
+    CUDA_TRY(cudaStreamSynchronize(c->stream));
+    return FP8BS_OK;
+}
+
+// ---- generators / conversions (host only) -------------------------------------------------
+uint8_t fp8bs_float_to_e4m3fn(float x) { return float_to_e4m3fn_rne(x); }
+float fp8bs_e4m3fn_to_float(uint8_t b) { return host_e4m3fn_to_float(b); }
+
+int fp8bs_gen_normal_e4m3(uint8_t* out, size_t n, uint64_t seed)
+{
+    if (!out) return FP8BS_ERR_NULL;
+    const uint64_t key = mix64(seed ^ 0xA5A5A5A5DEADBEEFull);
+    for (size_t i = 0; i < n; i += 2) {
+        // Box-Muller on two counter-based uniforms; element i and i+1 share one pair
+        const float u1 = u01(mix64(key + 2 * (i / 2))), u2 = u01(mix64(key + 2 * (i / 2) + 1));
+        const float r = std::sqrt(-2.0f * std::log(u1)), t = 6.28318530717958647692f * u2;
+        const float z[2] = {r * std::cos(t), r * std::sin(t)};
+        for (size_t j = 0; j < 2 && i + j < n; ++j) {
+            float v = z[j];
+            if (v > 240.0f) v = 240.0f;
+            if (v < -240.0f) v = -240.0f;
+            uint8_t b = float_to_e4m3fn_rne(v);
+            if ((b & 0x7F) < 0x08) b = 0;     // |x| < 2^-6 (all e4m3fn subnormals) -> +0
+            out[i + j] = b;
+        }
+    }
+    return FP8BS_OK;
+}
+
+int fp8bs_gen_uniform_f32(float* out, size_t n, uint64_t seed, float lo, float hi)
+{
+    if (!out) return FP8BS_ERR_NULL;
+    const uint64_t key = mix64(seed ^ 0x5C5C5C5C12345678ull);
+    for (size_t i = 0; i < n; ++i) {
+        const float u = static_cast<float>(mix64(key + i) >> 40) * (1.0f / 16777216.0f);   // [0,1)
+        float v = lo + (hi - lo) * u;
+        if (v >= hi) v = lo;
+        out[i] = v;
+    }
+    return FP8BS_OK;
+}
+
+int fp8bs_fnuz_to_fn(uint8_t* dst, const uint8_t* src, size_t n, size_t* bad_index)
+{
+    if (!dst || !src) return FP8BS_ERR_NULL;
+    for (size_t i = 0; i < n; ++i) {
+        const uint8_t b = src[i];
+        const int e = (b >> 3) & 0xF, m = b & 7;
+        uint8_t o;
+        if (b == 0x80) { if (bad_index) *bad_index = i; return FP8BS_ERR_FP8_BYTE; }   // NaN
+        if ((b & 0x7F) == 0) o = 0;
+        else if (e >= 2) o = static_cast<uint8_t>(b - 8);         // same mantissa, exponent field one lower
+        else {
+            // value = q * 2^-10 with q = m (e == 0) or 8 + m (e == 1); e4m3fn holds q/2 * 2^-9
+            const int q = (e == 0) ? m : 8 + m;
+            if (q & 1) { if (bad_index) *bad_index = i; return FP8BS_ERR_FP8_BYTE; }
+            o = static_cast<uint8_t>((b & 0x80) | (q / 2));       // q/2 in 1..7: an e4m3fn subnormal
+        }
+        dst[i] = o;
+    }
+    return FP8BS_OK;
+}
+
+}  // extern "C"

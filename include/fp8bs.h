@@ -1,0 +1,152 @@
+/*
+ * fp8bs.h -- C ABI of libfp8bs.so: the row-wise block-scaled FP8 GEMM for NVIDIA B200
+ *
+ *     C[M,N] (bf16, row-major) = sum_kb a_scale[m,kb] * b_scale[n/128,kb]
+ *                                       * ( A[m, kb*128 .. kb*128+127] . B[n, kb*128 .. kb*128+127] )
+ *
+ * Operand layouts are those of the reference kernels' 8-argument signature
+ * (mn_large.hip:11, mn_small.hip:10, check.cu:30-31):
+ *     A        fp8 e4m3, M x K column-major      A[m + M*k]
+ *     B        fp8 e4m3, N x K column-major      B[n + N*k]
+ *     a_scale  fp32 [M, K/128]                   a_scale[m + M*kb]
+ *     b_scale  fp32 [ceil(N/128), K/128]         b_scale[nb + ceil(N/128)*kb]
+ *     C        bf16, M x N row-major             C[m*N + n]
+ * fp8 bytes are OCP e4m3fn (the dialect B200 tensor cores read).  The reference stores
+ * e4m3fnuz; every value v with 2^-6 <= |v| <= 240 (and 0) exists in both dialects,
+ * with fn_byte = fnuz_byte - 8; fp8bs_fnuz_to_fn converts.
+ *
+ * All pointers passed to the fp8bs_gemm* functions are DEVICE pointers owned by the caller
+ * (as in the reference, where gemmGPU owns every buffer: check.cu:66-81, 122-128).  The
+ * library never allocates per call, launches asynchronously on the given stream and does
+ * not synchronise.  `stream` is a cudaStream_t passed as void* (NULL = default stream).
+ * There is no CPU fallback: without a B200-class device every call returns an error.
+ *
+ * Every function returns 0 on success or a negative FP8BS_ERR_* code; nothing throws or
+ * aborts.  Requirements: M, N, K > 0; K % 128 == 0 (mn_large.hip:17); M % 16 == 0 and
+ * N % 16 == 0 (16-byte strides of the column-major operands); A, B, C 16-byte aligned.
+ */
+#ifndef FP8BS_H
+#define FP8BS_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FP8BS_OK                  0
+#define FP8BS_ERR_NULL           -1   /* a required pointer is NULL */
+#define FP8BS_ERR_SHAPE          -2   /* M, N or K not positive, or K % 128 != 0 */
+#define FP8BS_ERR_ALIGN          -3   /* M % 16, N % 16 or a pointer alignment rule broken */
+#define FP8BS_ERR_WORKSPACE      -4   /* workspace missing or too small for the chosen path */
+#define FP8BS_ERR_ARG            -5   /* bad path / splits / tile / n0 argument */
+#define FP8BS_ERR_NO_DEVICE      -6   /* no usable sm_100 device or driver entry point */
+#define FP8BS_ERR_CUDA           -7   /* a CUDA runtime call failed; see fp8bs_last_cuda_error */
+#define FP8BS_ERR_DEVICE_TIMEOUT -8   /* a kernel gave up waiting on one of its barriers */
+#define FP8BS_ERR_FP8_BYTE       -9   /* an fp8 byte has no equal value in the other dialect */
+
+#define FP8BS_PATH_AUTO      0
+#define FP8BS_PATH_MN_LARGE  1   /* persistent full-K kernel   (role of mn_large.hip) */
+#define FP8BS_PATH_MN_SMALL  2   /* split-K kernel             (role of mn_small.hip) */
+
+/* ---- the operator ---------------------------------------------------------------- */
+
+/* Run-time shape dispatch between the two kernels.  Replaces the reference's manual,
+ * compile-time choice (which .hip file check.cu:13 / sgemm.cu:13 includes, plus OPTION,
+ * mn_large.hip:9; policy in README.md:99, 161).  Falls back to the best full-K
+ * configuration if the workspace is too small for split-K. */
+int fp8bs_gemm(const void* A, const void* B, const float* a_scale, const float* b_scale, void* C,
+               int M, int N, int K, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Forced large-M.N path: replaces in_smem_kernel<<<grid, block>>> (mn_large.hip:11;
+ * launch at check.cu:106-114).  Needs no workspace. */
+int fp8bs_gemm_mn_large(const void* A, const void* B, const float* a_scale, const float* b_scale,
+                        void* C, int M, int N, int K, void* stream);
+
+/* Forced small-M.N / large-K path: replaces k_large_kernel<<<grid, block>>> (mn_small.hip:10;
+ * launch at check.cu:92-101).  splits = 0 lets the library choose; 1 <= splits <= K/128.
+ * Partial sums are added in split order, so repeated calls give bit-identical C. */
+int fp8bs_gemm_mn_small(const void* A, const void* B, const float* a_scale, const float* b_scale,
+                        void* C, int M, int N, int K, int splits, void* workspace,
+                        size_t workspace_bytes, void* stream);
+
+/* Everything explicit.  For an N-shard of a wider problem (multi-GPU partition by columns):
+ * B and C hold columns [n0, n0+N) of an n_total-column problem, b_scale is the FULL
+ * [ceil(n_total/128), K/128] array, n0 % 64 == 0.  The plain operator is n0 = 0,
+ * n_total = N.  path: FP8BS_PATH_*; splits: 0 = choose; tile_n: 0 = choose, 128 or 256.
+ * No counterpart in the reference (it has no multi-GPU code); the arithmetic per element is
+ * check.cu:38-48 with cy replaced by n0 + cy in the b_scale index. */
+int fp8bs_gemm_ex(const void* A, const void* B, const float* a_scale, const float* b_scale, void* C,
+                  int M, int N, int K, int n0, int n_total, int path, int splits, int tile_n,
+                  void* workspace, size_t workspace_bytes, void* stream);
+
+/* One thread per C element, scalar fp32: the reference's ground-truth kernel restated in
+ * CUDA (ref_kernel, check.cu:30-49; gemmGPU option 2, check.cu:87-90).  Slow; for the
+ * on-device cross-check of the `check` program. */
+int fp8bs_gemm_ref(const void* A, const void* B, const float* a_scale, const float* b_scale,
+                   void* C, int M, int N, int K, void* stream);
+
+/* Pure host functions (no GPU needed).  fp8bs_select_path returns FP8BS_PATH_MN_LARGE or
+ * FP8BS_PATH_MN_SMALL (or a negative error) and stores the split count and tile width
+ * (either pointer may be NULL).  Replaces the geometry switch of check.cu:86-117. */
+int fp8bs_select_path(int M, int N, int K, int* splits, int* tile_n);
+
+/* Workspace the auto dispatch wants for this shape (0 if it would not split K), and the
+ * same for an explicit configuration.  The workspace must be zeroed once with
+ * fp8bs_workspace_init before its first use and after any FP8BS_ERR_DEVICE_TIMEOUT;
+ * calls re-arm it themselves.  Concurrent calls need distinct workspaces. */
+size_t fp8bs_workspace_bytes(int M, int N, int K);
+size_t fp8bs_workspace_bytes_ex(int M, int N, int K, int path, int splits, int tile_n);
+int fp8bs_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
+
+/* Synchronises `stream`, then returns FP8BS_OK or FP8BS_ERR_DEVICE_TIMEOUT if a kernel on
+ * the current device recorded a barrier timeout since the last call (and clears the
+ * record).  *detail (optional) receives the raw device status word. */
+int fp8bs_last_device_status(void* stream, unsigned int* detail);
+
+const char* fp8bs_status_string(int status);
+/* cudaError_t of the most recent failing CUDA call made by this thread (0 if none). */
+int fp8bs_last_cuda_error(void);
+/* Number of this library's kernels launched by this process so far. */
+unsigned long long fp8bs_launch_count(void);
+
+/* ---- host harness helpers (mirror the reference's utils.h / gemmGPU) --------------- */
+
+/* gemmGPU (check.cu:51-130): HOST buffers in, HOST bf16 C out; allocates device memory,
+ * copies, converts fp32 -> fp8 on the device (convert_float_to_fp8, check.cu:17-22),
+ * launches, copies back, frees.  A is fp32 M x K column-major, B fp32 N x K column-major.
+ * option 0 = auto dispatch, 1 = forced mn_small, 2 = the ref kernel (the reference's own
+ * option numbers, check.cu:86-117).  Synchronous. */
+int fp8bs_gemmGPU(uint16_t* C, const float* A, const float* B, const float* a_scale,
+                  const float* b_scale, size_t M, size_t N, size_t K, int option);
+
+/* The same end-to-end call for operands that are already fp8 bytes, with the device
+ * buffers and pinned staging owned by a reusable context (no allocation per call).
+ * Used for end-to-end timing: H2D of A, B and both scales, the GEMM, D2H of C. */
+typedef struct fp8bs_host_ctx fp8bs_host_ctx;
+int fp8bs_host_ctx_create(fp8bs_host_ctx** ctx, size_t max_M, size_t max_N, size_t max_K);
+int fp8bs_host_ctx_destroy(fp8bs_host_ctx* ctx);
+/* Pinned staging buffers of the context (valid until destroy): fill these, then call. */
+void* fp8bs_host_ctx_buffer(fp8bs_host_ctx* ctx, int which); /* 0 A, 1 B, 2 a_scale, 3 b_scale, 4 C */
+int fp8bs_gemm_host(fp8bs_host_ctx* ctx, uint16_t* C, const void* A, const void* B,
+                    const float* a_scale, const float* b_scale, int M, int N, int K);
+
+/* Seeded synthetic inputs (role of genMat, utils.h:25-33, but counter-based so that any
+ * slice can be generated independently).  Elements: N(0,1) rounded to nearest-even e4m3fn,
+ * clamped to |x| <= 240, |x| < 2^-6 flushed to +0 -- every value exists in e4m3fnuz too.
+ * Scales: uniform in [lo, hi). */
+int fp8bs_gen_normal_e4m3(uint8_t* out, size_t n, uint64_t seed);
+int fp8bs_gen_uniform_f32(float* out, size_t n, uint64_t seed, float lo, float hi);
+/* fp32 -> e4m3fn, round to nearest even, saturating to +-448; NaN -> 0x7F. */
+uint8_t fp8bs_float_to_e4m3fn(float x);
+float fp8bs_e4m3fn_to_float(uint8_t b);
+/* Re-encode e4m3fnuz bytes (the reference's element type, check.cu:17-21) as e4m3fn bytes
+ * of equal value.  Returns FP8BS_ERR_FP8_BYTE at the first byte whose value e4m3fn cannot
+ * hold (NaN 0x80, or an odd multiple of 2^-10 below 2^-6); *bad_index receives its index. */
+int fp8bs_fnuz_to_fn(uint8_t* dst, const uint8_t* src, size_t n, size_t* bad_index);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FP8BS_H */
