@@ -13,6 +13,7 @@ from .api import (  # noqa: F401
     PATH_AUTO,
     PATH_MN_LARGE,
     PATH_MN_SMALL,
+    TILE_PAIR,
     gemm,
     gemm_ref,
     gemmGPU,

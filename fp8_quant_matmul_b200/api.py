@@ -12,6 +12,7 @@ _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_PKG_DIR, "lib", "libfp8bs.so")
 
 PATH_AUTO, PATH_MN_LARGE, PATH_MN_SMALL = 0, 1, 2
+TILE_PAIR = 0x1000      # tile_n = 256 | TILE_PAIR: a 256 x 256 tile owned by a pair of CTAs
 
 # The 18 benchmark shapes (M, N, K) of the reference's results table (README.md:15-25).
 SHAPES_18 = [(m, n, k) for m in (1024, 6144)
@@ -46,7 +47,7 @@ _SIGS = {
     "fp8bs_host_ctx_create": (_c.c_int, [_c.POINTER(_c.c_void_p)] + [_c.c_size_t] * 3),
     "fp8bs_host_ctx_destroy": (_c.c_int, [_c.c_void_p]),
     "fp8bs_host_ctx_buffer": (_c.c_void_p, [_c.c_void_p, _c.c_int]),
-    "fp8bs_gemm_host": (_c.c_int, [_c.c_void_p] * 6 + [_c.c_int] * 3),
+    "fp8bs_gemm_host": (_c.c_int, [_c.c_void_p] * 6 + [_c.c_int] * 5),
     "fp8bs_gen_normal_e4m3": (_c.c_int, [_c.c_void_p, _c.c_size_t, _c.c_uint64]),
     "fp8bs_gen_uniform_f32": (_c.c_int, [_c.c_void_p, _c.c_size_t, _c.c_uint64, _c.c_float, _c.c_float]),
     "fp8bs_float_to_e4m3fn": (_c.c_uint8, [_c.c_float]),
@@ -155,6 +156,7 @@ def _torch():
 
 
 _workspaces = {}
+_retired = []
 
 
 def _workspace(device, nbytes):
@@ -163,6 +165,8 @@ def _workspace(device, nbytes):
     key = (device.type, device.index)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
+        if ws is not None:
+            _retired.append(ws)      # a captured CUDA graph may still point at the old one: keep it alive
         ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _check(lib().fp8bs_workspace_init(ws.data_ptr(), ws.numel(),
                                           torch.cuda.current_stream(device).cuda_stream), "fp8bs_workspace_init")
@@ -257,10 +261,11 @@ class HostContext:
         buf = (_c.c_uint8 * nbytes).from_address(ptr)
         return np.frombuffer(buf, dtype=dtype)
 
-    def gemm(self, C, A, B, a_scale, b_scale, M, N, K):
+    def gemm(self, C, A, B, a_scale, b_scale, M, N, K, n0=0, n_total=None):
         """Host pointers (numpy arrays, ideally views of the pinned buffers) in and out; synchronous."""
         _check(lib().fp8bs_gemm_host(self._h, C.ctypes.data, A.ctypes.data, B.ctypes.data, a_scale.ctypes.data,
-                                     b_scale.ctypes.data, M, N, K), "fp8bs_gemm_host")
+                                     b_scale.ctypes.data, M, N, K, n0, N if n_total is None else n_total),
+               "fp8bs_gemm_host")
         return C
 
     def close(self):

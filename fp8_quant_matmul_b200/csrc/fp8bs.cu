@@ -12,6 +12,7 @@
 #include <cmath>
 #include <cstdio>
 #include <cstring>
+#include <cstdlib>
 #include <mutex>
 #include <new>
 
@@ -39,6 +40,7 @@ __device__ unsigned int g_device_status[4];
 constexpr int MAX_DEVICES = 64;
 constexpr size_t COUNTER_BYTES = 65536;            // head of the workspace: 16384 tile counters
 constexpr int MAX_SPLITS = 32;
+constexpr size_t BSCALE_MAX_BYTES = 4u << 20;     // b_scale staging of the end-to-end context
 
 struct DeviceInfo {
     bool ready = false;
@@ -54,12 +56,17 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
                                   CUtensorMapFloatOOBfill);
 static EncodeTiledFn g_encode_tiled = nullptr;
+#ifdef FP8BS_PROFILE
+static long long* g_prof_buf = nullptr;
+#endif
 
-template <int BN, bool SPLITK>
+template <int BN, int CG, bool SPLITK>
 static int prepare_kernel()
 {
-    CUDA_TRY(cudaFuncSetAttribute(gemm_kernel<BN, SPLITK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  TileCfg<BN>::SMEM_BYTES));
+    CUDA_TRY(cudaFuncSetAttribute(gemm_kernel<BN, CG, SPLITK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  TileCfg<BN, CG>::SMEM_BYTES));
+    if (CG == 2)
+        CUDA_TRY(cudaFuncSetAttribute(gemm_kernel<BN, CG, SPLITK>, cudaFuncAttributeNonPortableClusterSizeAllowed, 0));
     return FP8BS_OK;
 }
 
@@ -95,8 +102,9 @@ static int device_setup(DeviceInfo** out)
             g_encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
         }
         int rc;
-        if ((rc = prepare_kernel<128, false>()) || (rc = prepare_kernel<256, false>()) ||
-            (rc = prepare_kernel<128, true>()) || (rc = prepare_kernel<256, true>())) {
+        if ((rc = prepare_kernel<128, 1, false>()) || (rc = prepare_kernel<256, 1, false>()) ||
+            (rc = prepare_kernel<256, 2, false>()) || (rc = prepare_kernel<128, 1, true>()) ||
+            (rc = prepare_kernel<256, 1, true>()) || (rc = prepare_kernel<256, 2, true>())) {
             d.status = rc;
             return rc;
         }
@@ -125,6 +133,7 @@ struct Config {
     int path;     // FP8BS_PATH_MN_LARGE / FP8BS_PATH_MN_SMALL
     int tile_n;   // 128 or 256
     int splits;   // 1 for mn_large
+    int cg;       // 1: a CTA owns 128 rows of a tile; 2: a pair of CTAs owns 256 rows
 };
 
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
@@ -132,44 +141,50 @@ static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 constexpr int SM_TARGET = 148;   // B200; the dispatch is a pure function of the shape
 
 // Estimated cost of a configuration in units of "one 128x128x128 block on one SM".
-static double config_cost(int M, int N, int K, int tile_n, int splits)
+static double config_cost(int M, int N, int K, int tile_n, int splits, int cg)
 {
     const int KB = K / 128;
-    const int tiles = ceil_div(M, 128) * ceil_div(N, tile_n);
+    const int tiles = ceil_div(M, 128 * cg) * ceil_div(N, tile_n);
     const int units = tiles * splits;
-    const int waves = ceil_div(units, SM_TARGET);
-    const double per_kb = (tile_n == 256) ? 2.0 : 1.2;       // a 128-wide tile re-reads A twice as often
+    const int waves = ceil_div(units, SM_TARGET / cg);
+    double per_kb = (tile_n == 256) ? 2.0 : 1.2;             // a 128-wide tile re-reads A twice as often
+    if (cg == 2) per_kb *= 0.9;                              // pairs fetch each B column once for 256 rows
     const double per_unit = ceil_div(KB, splits) * per_kb + 4.0 * (tile_n / 128);   // + prologue/epilogue
     double cost = waves * per_unit;
     if (splits > 1) cost += 3.0 + 0.75 * splits;             // partial-sum round trip through L2
     return cost;
 }
 
+// tile_n argument of the API: 0 = choose; 128 or 256 = tile width, one CTA per tile;
+// 256 | FP8BS_TILE_PAIR = 256 x 256 tile owned by a pair of CTAs.
 static Config choose_config(int M, int N, int K, int path, int splits, int tile_n)
 {
     const int KB = K / 128;
-    Config best{FP8BS_PATH_MN_LARGE, 128, 1};
+    Config best{FP8BS_PATH_MN_LARGE, 128, 1, 1};
     double best_cost = 1e300;
-    for (int tn = 128; tn <= 256; tn += 128) {
-        if (tile_n && tile_n != tn) continue;
-        const int smax = (path == FP8BS_PATH_MN_LARGE) ? 1 : (KB < MAX_SPLITS ? KB : MAX_SPLITS);
-        for (int s = 1; s <= smax; ++s) {
-            if (splits && s != splits) continue;
-            const double c = config_cost(M, N, K, tn, s);
-            if (c < best_cost) {
-                best_cost = c;
-                best = Config{(s > 1 || path == FP8BS_PATH_MN_SMALL) ? FP8BS_PATH_MN_SMALL : FP8BS_PATH_MN_LARGE, tn, s};
+    for (int cg = 1; cg <= 2; ++cg)
+        for (int tn = 128; tn <= 256; tn += 128) {
+            if (cg == 2 && tn != 256) continue;
+            if (tile_n && tile_n != (tn | (cg == 2 ? FP8BS_TILE_PAIR : 0))) continue;
+            const int smax = (path == FP8BS_PATH_MN_LARGE) ? 1 : (KB < MAX_SPLITS ? KB : MAX_SPLITS);
+            for (int s = 1; s <= smax; ++s) {
+                if (splits && s != splits) continue;
+                const double c = config_cost(M, N, K, tn, s, cg);
+                if (c < best_cost) {
+                    best_cost = c;
+                    best = Config{(s > 1 || path == FP8BS_PATH_MN_SMALL) ? FP8BS_PATH_MN_SMALL : FP8BS_PATH_MN_LARGE,
+                                  tn, s, cg};
+                }
             }
         }
-    }
     return best;
 }
 
 static size_t config_workspace(int M, int N, const Config& c)
 {
     if (c.path != FP8BS_PATH_MN_SMALL) return 0;
-    const size_t tiles = static_cast<size_t>(ceil_div(M, 128)) * ceil_div(N, c.tile_n);
-    return COUNTER_BYTES + tiles * c.splits * (static_cast<size_t>(c.tile_n) * 128 * sizeof(float));
+    const size_t half_tiles = static_cast<size_t>(ceil_div(M, 128 * c.cg)) * c.cg * ceil_div(N, c.tile_n);
+    return COUNTER_BYTES + half_tiles * c.splits * (static_cast<size_t>(c.tile_n) * 128 * sizeof(float));
 }
 
 static int check_shape(int M, int N, int K)
@@ -186,7 +201,7 @@ static int check_args(int M, int N, int K, int n0, int n_total, int path, int sp
     if (path < FP8BS_PATH_AUTO || path > FP8BS_PATH_MN_SMALL) return FP8BS_ERR_ARG;
     if (splits < 0 || splits > K / 128 || splits > MAX_SPLITS) return FP8BS_ERR_ARG;
     if (path == FP8BS_PATH_MN_LARGE && splits > 1) return FP8BS_ERR_ARG;
-    if (tile_n != 0 && tile_n != 128 && tile_n != 256) return FP8BS_ERR_ARG;
+    if (tile_n != 0 && tile_n != 128 && tile_n != 256 && tile_n != (256 | FP8BS_TILE_PAIR)) return FP8BS_ERR_ARG;
     if (n0 < 0 || n0 % 64 != 0 || n_total < n0 + N) return FP8BS_ERR_ARG;
     return FP8BS_OK;
 }
@@ -212,16 +227,74 @@ static int encode_operand_map(CUtensorMap* tm, const void* base, int mn, int K)
     return FP8BS_OK;
 }
 
-template <int BN, bool SPLITK>
-static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int sm_count,
-                  cudaStream_t stream)
+// a_scale as a 2-D fp32 tensor {M, K/128}; one box = the 128 scales of a tile's rows for one K block.
+static int encode_scale_map(CUtensorMap* tm, const float* base, int M, int KB)
 {
-    const int units = p.m_tiles * p.n_tiles * p.splits;
-    const int grid = units < sm_count ? units : sm_count;
-    gemm_kernel<BN, SPLITK><<<grid, TileCfg<BN>::THREADS, TileCfg<BN>::SMEM_BYTES, stream>>>(tmA, tmB, p);
-    g_launches.fetch_add(1, std::memory_order_relaxed);
-    CUDA_TRY(cudaGetLastError());
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(M), static_cast<cuuint64_t>(KB)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(M) * 4};
+    const cuuint32_t box[2] = {128u, 1u};
+    const cuuint32_t estr[2] = {1u, 1u};
+    const CUresult r = g_encode_tiled(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides,
+                                      box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                      CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        tl_last_cuda_error = static_cast<int>(r);
+        return FP8BS_ERR_CUDA;
+    }
     return FP8BS_OK;
+}
+
+// C as a 2-D bf16 tensor {N, M} (row-major M x N); a store box is 64 columns x 32 rows, 128-byte swizzled.
+static int encode_c_map(CUtensorMap* tm, void* base, int M, int N)
+{
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(M)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(N) * 2};
+    const cuuint32_t box[2] = {64u, 32u};
+    const cuuint32_t estr[2] = {1u, 1u};
+    const CUresult r = g_encode_tiled(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, estr,
+                                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        tl_last_cuda_error = static_cast<int>(r);
+        return FP8BS_ERR_CUDA;
+    }
+    return FP8BS_OK;
+}
+
+struct TensorMaps {
+    CUtensorMap A, B, As, C;
+};
+
+template <int BN, int CG, bool SPLITK>
+static int launch(const TensorMaps& tm, const GemmParams& p, int sm_count, cudaStream_t stream)
+{
+    using Cfg = TileCfg<BN, CG>;
+    const int units = p.m_tiles * p.n_tiles * p.splits;
+    const int groups = units < sm_count / CG ? units : sm_count / CG;    // tile walkers: CTAs or CTA pairs
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(groups * CG), 1, 1);
+    cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CG;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_kernel<BN, CG, SPLITK>, tm.A, tm.B, tm.As, tm.C, p);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    CUDA_TRY(e);
+    return FP8BS_OK;
+}
+
+template <bool SPLITK>
+static int launch_config(const Config& c, const TensorMaps& tm, const GemmParams& p, int sm_count, cudaStream_t st)
+{
+    if (c.cg == 2) return launch<256, 2, SPLITK>(tm, p, sm_count, st);
+    if (c.tile_n == 256) return launch<256, 1, SPLITK>(tm, p, sm_count, st);
+    return launch<128, 1, SPLITK>(tm, p, sm_count, st);
 }
 
 static int gemm_impl(const void* A, const void* B, const float* a_scale, const float* b_scale, void* C, int M,
@@ -233,13 +306,13 @@ static int gemm_impl(const void* A, const void* B, const float* a_scale, const f
     if (rc) return rc;
     if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15u)
         return FP8BS_ERR_ALIGN;
-    if ((reinterpret_cast<uintptr_t>(a_scale) | reinterpret_cast<uintptr_t>(b_scale)) & 3u) return FP8BS_ERR_ALIGN;
+    if ((reinterpret_cast<uintptr_t>(a_scale) & 15u) || (reinterpret_cast<uintptr_t>(b_scale) & 3u)) return FP8BS_ERR_ALIGN;
 
     Config cfg = choose_config(M, N, K, path, splits, tile_n);
     if (cfg.path == FP8BS_PATH_MN_SMALL) {
         const size_t need = config_workspace(M, N, cfg);
-        const size_t tiles = static_cast<size_t>(ceil_div(M, 128)) * ceil_div(N, cfg.tile_n);
-        const bool fits = workspace && workspace_bytes >= need && tiles <= COUNTER_BYTES / sizeof(unsigned int) &&
+        const size_t half_tiles = static_cast<size_t>(ceil_div(M, 128 * cfg.cg)) * cfg.cg * ceil_div(N, cfg.tile_n);
+        const bool fits = workspace && workspace_bytes >= need && half_tiles <= COUNTER_BYTES / sizeof(unsigned int) &&
                           (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0;
         if (!fits) {
             if (path != FP8BS_PATH_AUTO) return FP8BS_ERR_WORKSPACE;
@@ -251,12 +324,13 @@ static int gemm_impl(const void* A, const void* B, const float* a_scale, const f
     rc = device_setup(&dev);
     if (rc) return rc;
 
-    CUtensorMap tmA, tmB;
-    if ((rc = encode_operand_map(&tmA, A, M, K))) return rc;
-    if ((rc = encode_operand_map(&tmB, B, N, K))) return rc;
+    TensorMaps tm;
+    if ((rc = encode_operand_map(&tm.A, A, M, K))) return rc;
+    if ((rc = encode_operand_map(&tm.B, B, N, K))) return rc;
+    if ((rc = encode_scale_map(&tm.As, a_scale, M, K / 128))) return rc;
+    if ((rc = encode_c_map(&tm.C, C, M, N))) return rc;
 
     GemmParams p;
-    p.a_scale = a_scale;
     p.b_scale = b_scale;
     p.C = static_cast<__nv_bfloat16*>(C);
     p.partials = nullptr;
@@ -265,20 +339,27 @@ static int gemm_impl(const void* A, const void* B, const float* a_scale, const f
     p.M = M; p.N = N; p.K = K;
     p.n_off = n0;
     p.sn = ceil_div(n_total, 128);
-    p.m_tiles = ceil_div(M, 128);
+    p.m_tiles = ceil_div(M, 128 * cfg.cg);
     p.n_tiles = ceil_div(N, cfg.tile_n);
     p.splits = cfg.splits;
     p.elem_scale = 1.0f;
+#ifdef FP8BS_PROFILE
+    {
+        static long long* prof_buf = nullptr;       // profiling builds only: 8 counters per CTA, read by fp8bs_debug_prof
+        if (!prof_buf) cudaMalloc(&prof_buf, 16 * 1024 * sizeof(long long));
+        cudaMemsetAsync(prof_buf, 0, 16 * 1024 * sizeof(long long), static_cast<cudaStream_t>(stream));
+        p.prof = prof_buf;
+        g_prof_buf = prof_buf;
+    }
+#endif
     cudaStream_t st = static_cast<cudaStream_t>(stream);
 
     if (cfg.path == FP8BS_PATH_MN_SMALL) {
         p.counters = static_cast<unsigned int*>(workspace);
         p.partials = reinterpret_cast<float4*>(static_cast<char*>(workspace) + COUNTER_BYTES);
-        return cfg.tile_n == 256 ? launch<256, true>(tmA, tmB, p, dev->sm_count, st)
-                                 : launch<128, true>(tmA, tmB, p, dev->sm_count, st);
+        return launch_config<true>(cfg, tm, p, dev->sm_count, st);
     }
-    return cfg.tile_n == 256 ? launch<256, false>(tmA, tmB, p, dev->sm_count, st)
-                             : launch<128, false>(tmA, tmB, p, dev->sm_count, st);
+    return launch_config<false>(cfg, tm, p, dev->sm_count, st);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -446,7 +527,7 @@ int fp8bs_select_path(int M, int N, int K, int* splits, int* tile_n)
     if (rc) return rc;
     const Config c = choose_config(M, N, K, FP8BS_PATH_AUTO, 0, 0);
     if (splits) *splits = c.splits;
-    if (tile_n) *tile_n = c.tile_n;
+    if (tile_n) *tile_n = c.tile_n | (c.cg == 2 ? FP8BS_TILE_PAIR : 0);
     return c.path;
 }
 
@@ -504,6 +585,13 @@ const char* fp8bs_status_string(int status)
     }
 }
 
+#ifdef FP8BS_PROFILE
+int fp8bs_debug_prof(long long* out, int n)
+{
+    cudaDeviceSynchronize();
+    return cudaMemcpy(out, g_prof_buf, sizeof(long long) * n, cudaMemcpyDeviceToHost);
+}
+#endif
 int fp8bs_last_cuda_error(void) { return tl_last_cuda_error; }
 unsigned long long fp8bs_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
@@ -583,14 +671,14 @@ int fp8bs_host_ctx_create(fp8bs_host_ctx** out, size_t max_M, size_t max_N, size
     if (!c) return FP8BS_ERR_CUDA;
     std::memset(c, 0, sizeof(*c));
     c->max_M = max_M; c->max_N = max_N; c->max_K = max_K;
-    const size_t KB = max_K / 128, sn = (max_N + 127) / 128;
+    const size_t KB = max_K / 128;
     // split-K is only ever chosen for small M*N; 64 MiB covers every such configuration
     c->w_bytes = static_cast<size_t>(64) << 20;
     bool ok = cudaMalloc(&c->dA, max_M * max_K) == cudaSuccess && cudaMalloc(&c->dB, max_N * max_K) == cudaSuccess &&
-              cudaMalloc(&c->dAs, max_M * KB * 4) == cudaSuccess && cudaMalloc(&c->dBs, sn * KB * 4) == cudaSuccess &&
+              cudaMalloc(&c->dAs, max_M * KB * 4) == cudaSuccess && cudaMalloc(&c->dBs, BSCALE_MAX_BYTES) == cudaSuccess &&
               cudaMalloc(&c->dC, max_M * max_N * 2) == cudaSuccess && cudaMalloc(&c->dW, c->w_bytes) == cudaSuccess &&
               cudaMallocHost(&c->hA, max_M * max_K) == cudaSuccess && cudaMallocHost(&c->hB, max_N * max_K) == cudaSuccess &&
-              cudaMallocHost(&c->hAs, max_M * KB * 4) == cudaSuccess && cudaMallocHost(&c->hBs, sn * KB * 4) == cudaSuccess &&
+              cudaMallocHost(&c->hAs, max_M * KB * 4) == cudaSuccess && cudaMallocHost(&c->hBs, BSCALE_MAX_BYTES) == cudaSuccess &&
               cudaMallocHost(&c->hC, max_M * max_N * 2) == cudaSuccess &&
               cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) == cudaSuccess &&
               cudaMemset(c->dW, 0, COUNTER_BYTES) == cudaSuccess;
@@ -630,21 +718,22 @@ void* fp8bs_host_ctx_buffer(fp8bs_host_ctx* ctx, int which)
 }
 
 int fp8bs_gemm_host(fp8bs_host_ctx* ctx, uint16_t* C, const void* A, const void* B, const float* a_scale,
-                    const float* b_scale, int M, int N, int K)
+                    const float* b_scale, int M, int N, int K, int n0, int n_total)
 {
     if (!ctx || !C || !A || !B || !a_scale || !b_scale) return FP8BS_ERR_NULL;
     fp8bs_host_ctx_impl* c = reinterpret_cast<fp8bs_host_ctx_impl*>(ctx);
-    int rc = check_shape(M, N, K);
+    int rc = check_args(M, N, K, n0, n_total, FP8BS_PATH_AUTO, 0, 0);
     if (rc) return rc;
     if (static_cast<size_t>(M) > c->max_M || static_cast<size_t>(N) > c->max_N || static_cast<size_t>(K) > c->max_K)
         return FP8BS_ERR_SHAPE;
-    const size_t KB = K / 128, sn = (N + 127) / 128;
+    const size_t KB = K / 128, sn = (static_cast<size_t>(n_total) + 127) / 128;
+    if (sn * KB * 4 > BSCALE_MAX_BYTES) return FP8BS_ERR_SHAPE;
     CUDA_TRY(cudaMemcpyAsync(c->dA, A, static_cast<size_t>(M) * K, cudaMemcpyHostToDevice, c->stream));
     CUDA_TRY(cudaMemcpyAsync(c->dB, B, static_cast<size_t>(N) * K, cudaMemcpyHostToDevice, c->stream));
     CUDA_TRY(cudaMemcpyAsync(c->dAs, a_scale, static_cast<size_t>(M) * KB * 4, cudaMemcpyHostToDevice, c->stream));
     CUDA_TRY(cudaMemcpyAsync(c->dBs, b_scale, sn * KB * 4, cudaMemcpyHostToDevice, c->stream));
     rc = gemm_impl(c->dA, c->dB, static_cast<const float*>(c->dAs), static_cast<const float*>(c->dBs), c->dC, M, N, K,
-                   0, N, FP8BS_PATH_AUTO, 0, 0, c->dW, c->w_bytes, c->stream);
+                   n0, n_total, FP8BS_PATH_AUTO, 0, 0, c->dW, c->w_bytes, c->stream);
     if (rc) return rc;
     CUDA_TRY(cudaMemcpyAsync(C, c->dC, static_cast<size_t>(M) * N * 2, cudaMemcpyDeviceToHost, c->stream));
     CUDA_TRY(cudaStreamSynchronize(c->stream));

@@ -3,32 +3,43 @@
 // A is M x K column-major fp8 e4m3, B is N x K column-major fp8 e4m3, C is bf16 row-major
 // (the operand layouts of the reference kernels, mn_large.hip:11-15 and mn_small.hip:10-17).
 //
-// One kernel template serves both shape classes of the reference:
-//   SPLITK = false  "mn_large": persistent CTAs walk 128 x BN output tiles over the whole K
-//                   (replaces in_smem_kernel, mn_large.hip:11-128);
-//   SPLITK = true   "mn_small": each 128 x BN tile is cut into `splits` K ranges, partial
-//                   sums go to an fp32 workspace and the CTA that finishes a tile last adds
-//                   them in split order 0..S-1, so the result does not depend on timing
-//                   (replaces k_large_kernel, mn_small.hip:10-137, which instead shrinks
-//                   the tile to get more blocks).
+// One kernel template, three parameters:
+//   BN      width of the output tile (128 or 256 columns)
+//   CG      1: a CTA owns a 128 x BN tile.  2: two CTAs of a cluster own a 256 x BN tile; each
+//           loads its own 128 rows of A and its own half of the B columns, the leader issues
+//           tcgen05.mma.cta_group::2 (M = 256) that reads both CTAs' shared memory, and each
+//           CTA's TMEM receives its own 128 rows.  Halves the B traffic per output element.
+//   SPLITK  false "mn_large": persistent CTAs walk tiles over the whole K
+//                 (replaces in_smem_kernel, mn_large.hip:11-128);
+//           true  "mn_small": every tile is cut into `splits` K ranges, partial sums go to an
+//                 fp32 workspace and whoever finishes a tile last adds them in split order
+//                 0..S-1, so the result does not depend on timing (replaces k_large_kernel,
+//                 mn_small.hip:10-137, which instead shrinks the tile to get more blocks).
 //
-// Structure of a CTA (warp-specialised, no __syncthreads in the main loop):
-//   warp 0     TMA producer.  Both operands are MN-major in global memory, so a box of
-//              {128 m or n, 128 k} lands in shared memory as 128 rows (k) of 128 bytes,
-//              128-byte swizzled: the MN-major operand layout tcgen05.mma reads directly.
-//              The byte-wise transposing copy of the reference (mn_large.hip:40-48) has
-//              no counterpart here.
-//   warp 1     MMA issuer.  Per 128-K block: four tcgen05.mma kind::f8f6f4 (K = 32 each)
-//              into a fresh TMEM buffer (first one overwrites), then two commits: one
-//              frees the shared-memory stage, one publishes the TMEM buffer.
-//   warps 2..  promotion + epilogue.  TMEM lane = C row, so a thread owns one row and
-//              128 columns; per K block it reads the partial sums with tcgen05.ld and does
-//              acc = fma(a_scale*b_scale, partial, acc)   (mn_large.hip:99-106).
-//              The running sums stay in registers, so the MMA warp is already filling
-//              TMEM buffers for the next tile while these warps convert and store C.
-// All waits on mbarriers are bounded: on expiry the waiter raises a CTA-wide abort flag,
-// writes a code to the device status word and every role falls through to the common
-// exit, where TMEM is released.
+// Warp roles (no __syncthreads in the main loop; registers are moved from the first warpgroup
+// to the promotion warps with setmaxnreg):
+//   warp 0     TMA producer for A and B.  Both operands are MN-major in global memory, so a box
+//              of {128 m or n, 128 k} lands in shared memory as 128 rows (k) of 128 bytes,
+//              128-byte swizzled: the MN-major operand layout tcgen05.mma reads directly.  The
+//              byte-wise transposing copy of the reference (mn_large.hip:40-48) has no
+//              counterpart here.
+//   warp 1     MMA issuer.  Per 128-K block: four tcgen05.mma kind::f8f6f4 (K = 32 each) into a
+//              fresh TMEM buffer (the first one overwrites), then commits that free the
+//              shared-memory stage and publish the TMEM buffer.
+//   warp 2     TMA producer for a_scale: 128 floats per K block into a small ring, so the
+//              promotion warps never wait on a global load (mn_large.hip:50-55 stages the
+//              pre-multiplied scales in LDS for the same reason).
+//   warp 3     idle (completes the warpgroup that gives up its registers).
+//   warps 4..  promotion + epilogue.  TMEM lane = C row, so a thread owns one row and 128
+//              columns; per K block it reads the partial sums with tcgen05.ld (next chunk in
+//              flight while the current one is accumulated) and does
+//              acc = fma(a_scale*b_scale, partial, acc) two columns at a time (mn_large.hip:99-106).
+//              The running sums stay in registers, so the MMA warp is already filling TMEM for
+//              the next tile while these warps convert to bf16, stage through swizzled shared
+//              memory and hand C to TMA stores.
+// All waits on mbarriers are bounded: on expiry the waiter raises a CTA-wide abort flag, writes
+// a code to the device status word and every role falls through to the common exit, where TMEM
+// is released.
 #pragma once
 #include "ptx.cuh"
 #include <cuda_bf16.h>
@@ -43,46 +54,76 @@ enum : uint32_t {
     DS_TIMEOUT_STAGE_FULL = 2,   // MMA warp waited for TMA data
     DS_TIMEOUT_TMEM_EMPTY = 3,   // MMA warp waited for the promotion warps
     DS_TIMEOUT_TMEM_FULL = 4,    // promotion warps waited for the MMA warp
+    DS_TIMEOUT_SCALE_EMPTY = 5,  // scale producer waited for the promotion warps
+    DS_TIMEOUT_SCALE_FULL = 6,   // promotion warps waited for a_scale
 };
 
 struct GemmParams {
-    const float* a_scale;    // [M, K/128], m contiguous            (check.cu:46)
     const float* b_scale;    // [sn, K/128], nb contiguous          (check.cu:46)
     __nv_bfloat16* C;        // M x N row-major                     (check.cu:48)
-    float4* partials;        // split-K only: [unit][BN/4][128] float4
-    unsigned int* counters;  // split-K only: one arrival counter per tile, zero between calls
+    float4* partials;        // split-K only: [half-tile][split][BN/4][128] float4
+    unsigned int* counters;  // split-K only: one arrival counter per 128-row half-tile, zero between calls
     unsigned int* status;    // device status word
     int M, N, K;
     int n_off;               // global column index of local column 0 (N-sharded calls), else 0
     int sn;                  // rows of b_scale = ceil(N_total / 128)  (check.cu:36)
     int m_tiles, n_tiles, splits;
     float elem_scale;        // folded into b_scale: 1 for e4m3fn bytes
+#ifdef FP8BS_PROFILE
+    long long* prof;         // per CTA: 8 cycle counters (profiling builds only)
+#endif
 };
 
-template <int BN>
+template <int BN, int CG>
 struct TileCfg {
     static_assert(BN == 128 || BN == 256, "tile width");
-    static constexpr int BM = 128;
+    static_assert(CG == 1 || (CG == 2 && BN == 256), "pair tiles are 256 x 256");
+    static constexpr int BM = 128;                    // rows per CTA
+    static constexpr int TILE_M = BM * CG;            // rows per tile (pair of CTAs when CG == 2)
     static constexpr int BK = 128;                    // one scale block
     static constexpr int SLAB = 128 * 128;            // bytes of one {128 mn, 128 k} box
-    static constexpr int NBOX_B = BN / 128;
+    static constexpr int B_COLS = BN / CG;            // B columns this CTA loads
+    static constexpr int NBOX_B = B_COLS / 128;
     static constexpr int STAGE_BYTES = SLAB * (1 + NBOX_B);
-    static constexpr int STAGES = (BN == 256) ? 4 : 6;
     static constexpr int TMEM_COLS = 512;
     static constexpr int NBUF = TMEM_COLS / BN;       // TMEM partial-sum buffers
-    static constexpr int PROMO_WARPS = 4 * (BN / 128);
+    static constexpr int COLS = BN / 2;               // columns of the tile row a promotion thread owns (64 or 128)
+    static constexpr int NCH = COLS / 32;             // ... as 32-column chunks
+    static constexpr int PROMO_WARPS = 8;             // 4 TMEM lane quarters x 2 column groups
     static constexpr int PROMO_THREADS = 32 * PROMO_WARPS;
-    static constexpr int THREADS = 64 + PROMO_THREADS;
-    static constexpr int NUM_BARS = 2 * STAGES + 2 * NBUF;
-    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + NUM_BARS * 8 + 64;
+    static constexpr int THREADS = 128 + PROMO_THREADS;
+    static constexpr int STG_BYTES = PROMO_WARPS * 4096;   // per warp: one store box, 32 rows x 64 bf16 columns
+    static constexpr int SRING = 8;                   // a_scale ring entries (128 floats each)
+    static constexpr int SRING_BYTES = SRING * 512;
+    static constexpr int SMEM_LIMIT = 232448;         // 227 KB per CTA
+    static constexpr int FIXED = 1024 + STG_BYTES + SRING_BYTES + 512;
+    static constexpr int STAGES = (SMEM_LIMIT - FIXED) / STAGE_BYTES;
+    static_assert(STAGES >= 2, "pipeline depth");
+    static constexpr int NUM_BARS = 2 * STAGES + 2 * NBUF + 2 * SRING;
+    static_assert(NUM_BARS * 8 + 64 <= 512, "barrier area");
+    static constexpr int SMEM_BYTES = FIXED + STAGES * STAGE_BYTES;
 };
 
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;  // about one second
 
+#ifdef FP8BS_PROFILE
+#define PROF_DECL(name) long long name = 0
+#define PROF_T0() const long long prof_t0__ = clock64()
+#define PROF_ADD(name) name += clock64() - prof_t0__
+#define PROF_OUT(slot, name) p.prof[blockIdx.x * 16 + (slot)] = (name)
+__device__ __forceinline__ long long prof_now_ns() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return static_cast<long long>(t); }
+#define PROF_STAMP(slot) p.prof[blockIdx.x * 16 + (slot)] = prof_now_ns()
+#else
+#define PROF_DECL(name)
+#define PROF_T0()
+#define PROF_ADD(name)
+#define PROF_OUT(slot, name)
+#define PROF_STAMP(slot)
+#endif
+
 // Spin on an mbarrier phase with a time limit.  Returns false if the CTA is aborting.
-__device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity,
-                                             volatile uint32_t* abort_flag, unsigned int* status,
-                                             uint32_t code)
+__device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                             unsigned int* status, uint32_t code)
 {
     if (ptx::mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
@@ -99,114 +140,208 @@ __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity,
     }
 }
 
+// Two fp32 values in one 64-bit register, the operand form of fma.rn.f32x2 (low word = first value).
+__device__ __forceinline__ unsigned long long pack_f32x2(float lo, float hi)
+{
+    return static_cast<unsigned long long>(__float_as_uint(lo)) | (static_cast<unsigned long long>(__float_as_uint(hi)) << 32);
+}
+__device__ __forceinline__ float f32x2_lo(unsigned long long v) { return __uint_as_float(static_cast<uint32_t>(v)); }
+__device__ __forceinline__ float f32x2_hi(unsigned long long v) { return __uint_as_float(static_cast<uint32_t>(v >> 32)); }
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi)
 {
     __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);  // .x = lo (low half), round to nearest even
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
-template <int BN, bool SPLITK>
-__global__ void __launch_bounds__(TileCfg<BN>::THREADS, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-            const GemmParams p)
+// Two views of "64 consecutive fp32 columns of this thread's row": the packed accumulators of two
+// 32-column chunks, or a plain array.  pair(i) returns columns (2i, 2i+1).
+struct PackedCols {
+    const unsigned long long (&a)[16];
+    const unsigned long long (&b)[16];
+    __device__ __forceinline__ uint32_t bf16_pair(int i) const
+    {
+        const unsigned long long v = (i < 16) ? a[i & 15] : b[i & 15];
+        return pack_bf16x2(f32x2_lo(v), f32x2_hi(v));
+    }
+};
+struct FloatCols {
+    const float (&v)[64];
+    __device__ __forceinline__ uint32_t bf16_pair(int i) const { return pack_bf16x2(v[2 * i], v[2 * i + 1]); }
+};
+
+// Converts 64 columns of this thread's row to bf16 (round to nearest even) into a 32-row x 128-byte staging
+// box laid out as the 128-byte-swizzled TMA store expects; then the warp's lane 0 issues the store.
+// The box covers rows [row0, row0 + 32) and columns [col, col + 64); lane = row within the box.
+template <class Cols>
+__device__ __forceinline__ void stage_and_store_64(const CUtensorMap* tmC, uint8_t* stg, uint32_t stg_addr, int lane,
+                                                   const Cols cols, int col, int row0, int M, int N)
 {
-    using Cfg = TileCfg<BN>;
+    if (lane == 0) ptx::tma_store_wait_read<0>();      // the previous store out of this box has read it
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        uint4 q;
+        q.x = cols.bf16_pair(4 * j + 0);
+        q.y = cols.bf16_pair(4 * j + 1);
+        q.z = cols.bf16_pair(4 * j + 2);
+        q.w = cols.bf16_pair(4 * j + 3);
+        // row `lane` of the box, 16-byte chunk j, XOR-swizzled with the row index (bank-conflict free)
+        *reinterpret_cast<uint4*>(stg + lane * 128 + ((j ^ (lane & 7)) << 4)) = q;
+    }
+    ptx::fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0 && col < N && row0 < M) {
+        ptx::tma_store_2d(tmC, stg_addr, col, row0);   // rows >= M and columns >= N are clipped by the hardware
+        ptx::tma_store_commit();
+    }
+}
+
+template <int BN, int CG, bool SPLITK>
+__global__ void __launch_bounds__(TileCfg<BN, CG>::THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+            const __grid_constant__ CUtensorMap tmAs, const __grid_constant__ CUtensorMap tmC, const GemmParams p)
+{
+    using Cfg = TileCfg<BN, CG>;
     constexpr int STAGES = Cfg::STAGES;
     constexpr int NBUF = Cfg::NBUF;
+    constexpr int SRING = Cfg::SRING;
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = ptx::smem_u32(smem_raw);
     const uint32_t stage_base = (raw + 1023u) & ~1023u;   // swizzle atoms need 1024-byte alignment
     uint8_t* aligned = smem_raw + (stage_base - raw);
-    const uint32_t bar_base = stage_base + STAGES * Cfg::STAGE_BYTES;
-    volatile uint32_t* ctrl =
-        reinterpret_cast<volatile uint32_t*>(aligned + STAGES * Cfg::STAGE_BYTES + Cfg::NUM_BARS * 8);
+    // layout: [stages][epilogue staging][a_scale ring][barriers + control words]
+    const uint32_t stg_base = stage_base + STAGES * Cfg::STAGE_BYTES;
+    uint8_t* stg_ptr = aligned + STAGES * Cfg::STAGE_BYTES;
+    const uint32_t sring_base = stg_base + Cfg::STG_BYTES;
+    const float* sring_ptr = reinterpret_cast<const float*>(stg_ptr + Cfg::STG_BYTES);
+    const uint32_t bar_base = sring_base + Cfg::SRING_BYTES;
+    volatile uint32_t* ctrl = reinterpret_cast<volatile uint32_t*>(stg_ptr + Cfg::STG_BYTES + Cfg::SRING_BYTES +
+                                                                    Cfg::NUM_BARS * 8);
     // ctrl[0] TMEM base address, ctrl[1] abort flag, ctrl[2] "this CTA reduces the tile"
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
     auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
     auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + NBUF + b); };
+    auto sfull_bar = [&](int i) { return bar_base + 8u * (2 * STAGES + 2 * NBUF + i); };
+    auto sempty_bar = [&](int i) { return bar_base + 8u * (2 * STAGES + 2 * NBUF + SRING + i); };
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) { PROF_STAMP(8); }
+    const uint32_t rank = (CG == 2) ? ptx::cluster_ctarank() : 0u;     // 0 = leader of the pair
+    const int group_id = blockIdx.x / CG;                               // which tile walker this CTA belongs to
+    const int num_groups = gridDim.x / CG;
 
     if (threadIdx.x == 0) {
         ptx::prefetch_tensormap(&tmA);
         ptx::prefetch_tensormap(&tmB);
+        ptx::prefetch_tensormap(&tmAs);
+        ptx::prefetch_tensormap(&tmC);
         for (int s = 0; s < STAGES; ++s) {
             ptx::mbar_init(full_bar(s), 1);
             ptx::mbar_init(empty_bar(s), 1);
         }
         for (int b = 0; b < NBUF; ++b) {
             ptx::mbar_init(tfull_bar(b), 1);
-            ptx::mbar_init(tempty_bar(b), Cfg::PROMO_WARPS);
+            ptx::mbar_init(tempty_bar(b), Cfg::PROMO_WARPS * CG);   // the leader also hears from the peer's warps
+        }
+        for (int i = 0; i < SRING; ++i) {
+            ptx::mbar_init(sfull_bar(i), 1);
+            ptx::mbar_init(sempty_bar(i), Cfg::PROMO_WARPS);
         }
         ctrl[1] = 0u;
         ctrl[2] = 0u;
         ptx::fence_mbar_init();
     }
     if (warp == 1) {
-        ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(&ctrl[0])), Cfg::TMEM_COLS);
-        ptx::tmem_relinquish();
+        if constexpr (CG == 2) {
+            ptx::tmem_alloc_pair(ptx::smem_u32(const_cast<uint32_t*>(&ctrl[0])), Cfg::TMEM_COLS);
+            ptx::tmem_relinquish_pair();
+        } else {
+            ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(&ctrl[0])), Cfg::TMEM_COLS);
+            ptx::tmem_relinquish();
+        }
     }
     ptx::tc_fence_before_sync();
     __syncthreads();
+    if constexpr (CG == 2) ptx::cluster_sync();      // the peer's barriers exist before anything remote touches them
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = ctrl[0];
     volatile uint32_t* abort_flag = &ctrl[1];
+    if (threadIdx.x == 0) { PROF_STAMP(9); }
 
     const int KB = p.K / Cfg::BK;
     const int units = p.m_tiles * p.n_tiles * p.splits;
 
-    // unit -> (tile, split) -> (m0, n0, kb range).  Tiles are numbered m-fastest so CTAs that
-    // run side by side share the (wider) B slab through L2.
+    // unit -> (tile, split) -> (row of this CTA, first column, K-block range).  Tiles are numbered
+    // m-fastest so CTAs that run side by side share the B slab through L2.
     auto decode = [&](int u, int& tile, int& m0, int& n0, int& kb0, int& kb1) {
         const int split = SPLITK ? (u % p.splits) : 0;
         tile = SPLITK ? (u / p.splits) : u;
-        m0 = (tile % p.m_tiles) * Cfg::BM;
+        m0 = (tile % p.m_tiles) * Cfg::TILE_M + static_cast<int>(rank) * Cfg::BM;
         n0 = (tile / p.m_tiles) * BN;
         kb0 = SPLITK ? (split * KB) / p.splits : 0;
         kb1 = SPLITK ? ((split + 1) * KB) / p.splits : KB;
     };
 
-    if (warp == 0) {
-        // ------------------------------------------------------------ TMA producer ----
-        if (lane == 0) {
+    if (warp < 4) {
+        ptx::setmaxnreg_dec<56>();
+        if (warp == 0 && lane == 0) {
+            // ---------------------------------------------------- TMA producer: A and B ----
             uint32_t it = 0;
             bool ok = true;
-            for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+            PROF_DECL(w_empty);
+            for (int u = group_id; u < units && ok; u += num_groups) {
                 int tile, m0, n0, kb0, kb1;
                 decode(u, tile, m0, n0, kb0, kb1);
-                int nbox = (p.N - n0 + 127) >> 7;          // B slabs that hold any real column
-                nbox = nbox < Cfg::NBOX_B ? nbox : Cfg::NBOX_B;
+                const int nb0 = n0 + static_cast<int>(rank) * Cfg::B_COLS;    // first B column this CTA loads
+                int nbox = (p.N - nb0 + 127) >> 7;                            // B slabs that hold any real column
+                nbox = nbox < 0 ? 0 : (nbox < Cfg::NBOX_B ? nbox : Cfg::NBOX_B);
+                if (CG == 2) nbox = Cfg::NBOX_B;                              // pairs: fixed byte count (zero fill)
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1u;
+                    { PROF_T0();
                     ok = wait_bounded(empty_bar(s), ph ^ 1u, abort_flag, p.status, DS_TIMEOUT_STAGE_EMPTY);
+                    PROF_ADD(w_empty); }
                     if (!ok) break;
                     const uint32_t a_dst = stage_base + s * Cfg::STAGE_BYTES;
-                    ptx::mbar_arrive_expect_tx(full_bar(s), Cfg::SLAB * (1 + nbox));
-                    ptx::tma_load_2d(a_dst, &tmA, m0, kb * Cfg::BK, full_bar(s));
-                    for (int j = 0; j < nbox; ++j)
-                        ptx::tma_load_2d(a_dst + Cfg::SLAB * (1 + j), &tmB, n0 + 128 * j, kb * Cfg::BK,
-                                         full_bar(s));
+                    if constexpr (CG == 2) {
+                        // both CTAs' bytes are counted on the leader's barrier, which the MMA warp waits on
+                        const uint32_t lead_full = ptx::mapa(full_bar(s), 0);
+                        if (rank == 0) ptx::mbar_arrive_expect_tx(full_bar(s), 2 * Cfg::STAGE_BYTES);
+                        ptx::tma_load_2d_pair(a_dst, &tmA, m0, kb * Cfg::BK, lead_full);
+                        for (int j = 0; j < Cfg::NBOX_B; ++j)
+                            ptx::tma_load_2d_pair(a_dst + Cfg::SLAB * (1 + j), &tmB, nb0 + 128 * j, kb * Cfg::BK, lead_full);
+                    } else {
+                        ptx::mbar_arrive_expect_tx(full_bar(s), Cfg::SLAB * (1 + nbox));
+                        ptx::tma_load_2d(a_dst, &tmA, m0, kb * Cfg::BK, full_bar(s));
+                        for (int j = 0; j < nbox; ++j)
+                            ptx::tma_load_2d(a_dst + Cfg::SLAB * (1 + j), &tmB, nb0 + 128 * j, kb * Cfg::BK, full_bar(s));
+                    }
                 }
             }
+            PROF_OUT(0, w_empty);
             if (!ok) {
-                // Aborting with loads possibly in flight: give them a bounded time to land
-                // before the shared memory can be handed to another CTA.
+                // Aborting with loads possibly in flight: give them a bounded time to land before the
+                // shared memory can be handed to another CTA.
                 const long long t0 = clock64();
                 while (clock64() - t0 < 2000000LL) __nanosleep(1000);
             }
-        }
-        __syncwarp();
-    } else if (warp == 1) {
-        // ------------------------------------------------------------ MMA issuer ------
-        if (lane == 0) {
-            constexpr uint32_t idesc = ptx::make_idesc_e4m3_mnmajor(Cfg::BM, BN);
+        } else if (warp == 1 && lane == 0 && rank == 0) {
+            // ---------------------------------------------------- MMA issuer ----------------
+            constexpr uint32_t idesc = ptx::make_idesc_e4m3_mnmajor(Cfg::TILE_M, BN);
             uint32_t it = 0, ait = 0;
             bool ok = true;
-            for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+            PROF_DECL(w_tempty); PROF_DECL(w_full); PROF_DECL(t_mma_total);
+#ifdef FP8BS_PROFILE
+            const long long mma_start = clock64();
+#endif
+            uint32_t peer_base = 0;
+            if constexpr (CG == 2) peer_base = ptx::mapa(bar_base, 1) - bar_base;   // offset to the peer's window
+            for (int u = group_id; u < units && ok; u += num_groups) {
                 int tile, m0, n0, kb0, kb1;
                 decode(u, tile, m0, n0, kb0, kb1);
                 for (int kb = kb0; kb < kb1; ++kb, ++it, ++ait) {
@@ -214,10 +349,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     const uint32_t ph = (it / STAGES) & 1u;
                     const int b = ait % NBUF;
                     const uint32_t bph = (ait / NBUF) & 1u;
+                    { PROF_T0();
                     ok = wait_bounded(tempty_bar(b), bph ^ 1u, abort_flag, p.status, DS_TIMEOUT_TMEM_EMPTY);
+                    PROF_ADD(w_tempty); }
                     if (!ok) break;
+                    { PROF_T0();
                     ok = wait_bounded(full_bar(s), ph, abort_flag, p.status, DS_TIMEOUT_STAGE_FULL);
+                    PROF_ADD(w_full); }
                     if (!ok) break;
+#ifdef FP8BS_PROFILE
+                    if (it == 0) { PROF_STAMP(10); }
+#endif
                     ptx::tc_fence_after_sync();
                     const uint32_t a_addr = stage_base + s * Cfg::STAGE_BYTES;
                     const uint64_t adesc = ptx::make_smem_desc_sw128(a_addr, Cfg::SLAB, 1024);
@@ -226,102 +368,165 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         // K = 32 per instruction = 4 swizzle atoms of 8 k-rows = 4096 bytes
-                        ptx::mma_f8f6f4(d, adesc + static_cast<uint64_t>(j * (4096 >> 4)),
-                                        bdesc + static_cast<uint64_t>(j * (4096 >> 4)), idesc, j > 0 ? 1u : 0u);
+                        const uint64_t step = static_cast<uint64_t>(j * (4096 >> 4));
+                        if constexpr (CG == 2) ptx::mma_f8f6f4_pair(d, adesc + step, bdesc + step, idesc, j > 0 ? 1u : 0u);
+                        else ptx::mma_f8f6f4(d, adesc + step, bdesc + step, idesc, j > 0 ? 1u : 0u);
                     }
-                    ptx::mma_commit(empty_bar(s));
-                    ptx::mma_commit(tfull_bar(b));
+                    if constexpr (CG == 2) {
+                        ptx::mma_commit_pair(empty_bar(s));
+                        ptx::mma_commit_pair(empty_bar(s) + peer_base);
+                        ptx::mma_commit_pair(tfull_bar(b));
+                        ptx::mma_commit_pair(tfull_bar(b) + peer_base);
+                    } else {
+                        ptx::mma_commit(empty_bar(s));
+                        ptx::mma_commit(tfull_bar(b));
+                    }
+                }
+            }
+#ifdef FP8BS_PROFILE
+            t_mma_total = clock64() - mma_start;
+#endif
+            PROF_OUT(1, w_tempty); PROF_OUT(2, w_full); PROF_OUT(3, t_mma_total); PROF_STAMP(11);
+        } else if (warp == 2 && lane == 0) {
+            // ---------------------------------------------------- TMA producer: a_scale ----
+            uint32_t sit = 0;
+            bool ok = true;
+            for (int u = group_id; u < units && ok; u += num_groups) {
+                int tile, m0, n0, kb0, kb1;
+                decode(u, tile, m0, n0, kb0, kb1);
+                for (int kb = kb0; kb < kb1; ++kb, ++sit) {
+                    const int i = sit % SRING;
+                    const uint32_t ph = (sit / SRING) & 1u;
+                    ok = wait_bounded(sempty_bar(i), ph ^ 1u, abort_flag, p.status, DS_TIMEOUT_SCALE_EMPTY);
+                    if (!ok) break;
+                    ptx::mbar_arrive_expect_tx(sfull_bar(i), 512);
+                    ptx::tma_load_2d(sring_base + i * 512, &tmAs, m0, kb, sfull_bar(i));   // rows >= M read as 0
                 }
             }
         }
         __syncwarp();
     } else {
-        // ------------------------------------------------------------ promotion -------
-        const int pw = warp - 2;
+        // -------------------------------------------------------- promotion + epilogue ------
+        ptx::setmaxnreg_inc<224>();
+        const int pw = warp - 4;
         const int quarter = warp & 3;            // TMEM lanes this warp may read: 32*quarter ..
-        const int grp = pw >> 2;                 // which 128 columns of the tile
+        const int grp = pw >> 2;                 // which half of the tile's columns
         const int row_in_tile = quarter * 32 + lane;
+        uint8_t* my_stg = stg_ptr + pw * 4096;
+        const uint32_t my_stg_addr = stg_base + pw * 4096;
+        uint32_t lead_tempty = tempty_bar(0);
+        if constexpr (CG == 2) lead_tempty = ptx::mapa(tempty_bar(0), 0);
         uint32_t ait = 0;
         bool ok = true;
-        for (int u = blockIdx.x; u < units; u += gridDim.x) {
+        PROF_DECL(w_sfull); PROF_DECL(w_tfull); PROF_DECL(t_fma); PROF_DECL(t_epi);
+        for (int u = group_id; u < units; u += num_groups) {
             int tile, m0, n0, kb0, kb1;
             decode(u, tile, m0, n0, kb0, kb1);
-            const int m = m0 + row_in_tile;
-            const bool mvalid = m < p.M;
-            const int ncol0 = n0 + grp * 128;                 // first local column of this thread
+            const int ncol0 = n0 + grp * Cfg::COLS;           // first local column of this thread
             const int gcol0 = p.n_off + ncol0;                // its global column (b_scale index)
-            int nb_lo = gcol0 >> 7, nb_hi = (gcol0 + 127) >> 7;
+            int nb_lo = gcol0 >> 7, nb_hi = (gcol0 >> 7) + 1;  // a thread's columns touch at most two 128-blocks
             nb_lo = nb_lo < p.sn ? nb_lo : p.sn - 1;
             nb_hi = nb_hi < p.sn ? nb_hi : p.sn - 1;
             const int hi_from = 4 - ((gcol0 & 127) >> 5);     // first 32-col chunk that uses nb_hi
 
-            float acc[128];
+            // running sums of this thread's row: 4 chunks of 32 columns, two fp32 per 64-bit register
+            unsigned long long acc[Cfg::NCH][16];
 #pragma unroll
-            for (int i = 0; i < 128; ++i) acc[i] = 0.0f;
+            for (int c = 0; c < Cfg::NCH; ++c)
+#pragma unroll
+                for (int i = 0; i < 16; ++i) acc[c][i] = 0ull;
 
-            const float* as_ptr = p.a_scale + (mvalid ? m : 0);
-            float as_n = mvalid ? __ldg(as_ptr + static_cast<size_t>(kb0) * p.M) : 0.0f;
-            float bl_n = __ldg(p.b_scale + nb_lo + static_cast<size_t>(kb0) * p.sn);
-            float bh_n = __ldg(p.b_scale + nb_hi + static_cast<size_t>(kb0) * p.sn);
+            // b_scale is tiny and warp-uniform.  Lane l holds the values of K block (base + l); every 32 blocks
+            // the vector loaded one round earlier takes over, so no iteration waits on a global load.
+            const float* bl_ptr = p.b_scale + nb_lo;
+            const float* bh_ptr = p.b_scale + nb_hi;
+            auto load_bvec = [&](const float* ptr, int kbase) {
+                const int k = kbase + lane;
+                return (k < kb1) ? __ldg(ptr + static_cast<size_t>(k) * p.sn) : 0.0f;
+            };
+            float bl_vec = load_bvec(bl_ptr, kb0), bh_vec = load_bvec(bh_ptr, kb0);
+            float bl_nxt = load_bvec(bl_ptr, kb0 + 32), bh_nxt = load_bvec(bh_ptr, kb0 + 32);
 
             for (int kb = kb0; kb < kb1 && ok; ++kb, ++ait) {
-                const float s_lo = as_n * (bl_n * p.elem_scale);
-                const float s_hi = as_n * (bh_n * p.elem_scale);
-                if (kb + 1 < kb1) {   // next block's scales, in flight while we wait for TMEM
-                    as_n = mvalid ? __ldg(as_ptr + static_cast<size_t>(kb + 1) * p.M) : 0.0f;
-                    bl_n = __ldg(p.b_scale + nb_lo + static_cast<size_t>(kb + 1) * p.sn);
-                    bh_n = __ldg(p.b_scale + nb_hi + static_cast<size_t>(kb + 1) * p.sn);
+                const int kj = (kb - kb0) & 31;
+                if (kj == 0 && kb != kb0) {
+                    bl_vec = bl_nxt;
+                    bh_vec = bh_nxt;
+                    bl_nxt = load_bvec(bl_ptr, kb + 32);
+                    bh_nxt = load_bvec(bh_ptr, kb + 32);
                 }
-                const int b = ait % NBUF;
-                const uint32_t bph = (ait / NBUF) & 1u;
-                ok = wait_bounded(tfull_bar(b), bph, abort_flag, p.status, DS_TIMEOUT_TMEM_FULL);
+                const float bl = __shfl_sync(0xffffffffu, bl_vec, kj) * p.elem_scale;
+                const float bh = __shfl_sync(0xffffffffu, bh_vec, kj) * p.elem_scale;
+                // a_scale of this row and block, from the ring
+                const int si = ait % SRING;
+                { PROF_T0();
+                ok = wait_bounded(sfull_bar(si), (ait / SRING) & 1u, abort_flag, p.status, DS_TIMEOUT_SCALE_FULL);
+                PROF_ADD(w_sfull); }
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
+                const float as = sring_ptr[si * 128 + row_in_tile];     // released at the end of the iteration
+                const float s_lo = as * bl, s_hi = as * bh;
+
+                const int b = ait % NBUF;
+                { PROF_T0();
+                ok = wait_bounded(tfull_bar(b), (ait / NBUF) & 1u, abort_flag, p.status, DS_TIMEOUT_TMEM_FULL);
+                PROF_ADD(w_tfull); }
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                PROF_T0();
                 ptx::tc_fence_after_sync();
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                                       static_cast<uint32_t>(b * BN + grp * 128);
+                                       static_cast<uint32_t>(b * BN + grp * Cfg::COLS);
+                // partial sums -> registers, 64 columns per load.  Each load and its wait are one asm statement:
+                // the destination registers of a tcgen05.ld are written asynchronously, and code the compiler
+                // places between a load and its wait (a spill, a move) would read them too early.
+                const unsigned long long s_lo2 = pack_f32x2(s_lo, s_lo), s_hi2 = pack_f32x2(s_hi, s_hi);
+                uint32_t v[64];
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t v[32];
-                    ptx::tmem_ld_x32(taddr + c * 32, v);
-                    ptx::tmem_ld_wait();
-                    const float sc = (c >= hi_from) ? s_hi : s_lo;
-#pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        acc[c * 32 + i] = fmaf(sc, __uint_as_float(v[i]), acc[c * 32 + i]);
+                for (int q = 0; q < Cfg::COLS / 64; ++q) {
+                    ptx::tmem_ld_x64_sync(taddr + q * 64, v);
+                    ptx::fma32_from64_0(acc[2 * q], v, (2 * q >= hi_from) ? s_hi2 : s_lo2);
+                    ptx::fma32_from64_32(acc[2 * q + 1], v, (2 * q + 1 >= hi_from) ? s_hi2 : s_lo2);
                 }
+                // Release the TMEM buffer and the a_scale ring entry only now, after the FMAs that consumed them.
+                // An arrive placed straight after the shared-memory read of a_scale (its value not yet used) let
+                // the producer refill the entry before a slow warp's read had completed: rare 32-row blocks scaled
+                // with the a_scale of the work unit eight K blocks later.
                 ptx::tc_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(tempty_bar(b));
+                if (lane == 0) {
+                    if constexpr (CG == 2) ptx::mbar_arrive_cluster(lead_tempty + 8u * b);
+                    else ptx::mbar_arrive(tempty_bar(b));
+                    ptx::mbar_arrive(sempty_bar(si));
+                }
+                PROF_ADD(t_fma);
             }
+#ifdef FP8BS_PROFILE
+            const long long epi_start = clock64();
+            if (pw == 0 && lane == 0) { PROF_STAMP(12); }
+#endif
 
             if constexpr (!SPLITK) {
                 if (!ok) break;
-                // ---- epilogue: fp32 -> bf16 (round to nearest even), 16-byte stores ----
-                if (mvalid) {
-                    __nv_bfloat16* crow = p.C + static_cast<size_t>(m) * p.N + ncol0;
+                // ---- epilogue: fp32 -> bf16 (round to nearest even), staged, TMA store ----
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        if (ncol0 + j * 8 < p.N) {
-                            uint4 q;
-                            q.x = pack_bf16x2(acc[j * 8 + 0], acc[j * 8 + 1]);
-                            q.y = pack_bf16x2(acc[j * 8 + 2], acc[j * 8 + 3]);
-                            q.z = pack_bf16x2(acc[j * 8 + 4], acc[j * 8 + 5]);
-                            q.w = pack_bf16x2(acc[j * 8 + 6], acc[j * 8 + 7]);
-                            *reinterpret_cast<uint4*>(crow + j * 8) = q;
-                        }
-                    }
-                }
+                for (int h = 0; h < Cfg::COLS / 64; ++h)
+                    stage_and_store_64(&tmC, my_stg, my_stg_addr, lane, PackedCols{acc[2 * h], acc[2 * h + 1]},
+                                       ncol0 + h * 64, m0 + quarter * 32, p.M, p.N);
             } else {
                 // ---- split-K: publish this K range's partial sums ----
-                // Layout [unit][column quad][row]: a warp's 32 rows of one column quad are
-                // 512 contiguous bytes, for the writes here and the reads below alike.
-                float4* part = p.partials + (static_cast<size_t>(u) * (BN / 4) + grp * 32) * 128 + row_in_tile;
+                // One 128-row half-tile per CTA.  Layout [half-tile][split][column quad][row]: a warp's
+                // 32 rows of one column quad are 512 contiguous bytes, for the writes here and the reads below.
+                const int split = u % p.splits;
+                const int half_tile = tile * CG + static_cast<int>(rank);
+                float4* part = p.partials +
+                               ((static_cast<size_t>(half_tile) * p.splits + split) * (BN / 4) + grp * (Cfg::COLS / 4)) * 128 + row_in_tile;
                 if (ok) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j)
+                    for (int j = 0; j < Cfg::COLS / 4; ++j)
                         part[static_cast<size_t>(j) * 128] =
-                            make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+                            make_float4(f32x2_lo(acc[j / 8][(2 * j) % 16]), f32x2_hi(acc[j / 8][(2 * j) % 16]),
+                                        f32x2_lo(acc[j / 8][(2 * j + 1) % 16]), f32x2_hi(acc[j / 8][(2 * j + 1) % 16]));
                     __threadfence();
                 }
                 // Every promotion thread reaches this barrier, aborting or not.
@@ -340,9 +545,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 }
                 if (any_fail) { ok = false; break; }
                 if (pw == 0 && lane == 0) {
-                    const unsigned int old = atomicAdd(&p.counters[tile], 1u);
+                    __threadfence();      // the partial sums of the whole CTA (seen through the barrier) before the ticket
+                    const unsigned int old = atomicAdd(&p.counters[half_tile], 1u);
                     const bool last = (old == static_cast<unsigned int>(p.splits - 1));
-                    if (last) p.counters[tile] = 0u;     // every split has arrived: re-arm for the next call
+                    if (last) p.counters[half_tile] = 0u;     // every split has arrived: re-arm for the next call
                     ctrl[2] = last ? 1u : 0u;
                 }
                 asm volatile("barrier.cta.sync.aligned 1, %0;" ::"n"(Cfg::PROMO_THREADS) : "memory");
@@ -350,51 +556,51 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     __threadfence();
                     // ---- deterministic reduction: splits are added in the order 0, 1, .., S-1 ----
                     const float4* base = p.partials +
-                        (static_cast<size_t>(tile) * p.splits * (BN / 4) + grp * 32) * 128 + row_in_tile;
+                        (static_cast<size_t>(half_tile) * p.splits * (BN / 4) + grp * (Cfg::COLS / 4)) * 128 + row_in_tile;
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        float sum[32];
+                    for (int h = 0; h < Cfg::COLS / 64; ++h) {
+                        float sum[64];
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) sum[i] = 0.0f;
+                        for (int i = 0; i < 64; ++i) sum[i] = 0.0f;
                         for (int s = 0; s < p.splits; ++s) {
                             const float4* ps = base + static_cast<size_t>(s) * (BN / 4) * 128;
 #pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                const float4 v = __ldcg(ps + static_cast<size_t>(c * 8 + j) * 128);
+                            for (int j = 0; j < 16; ++j) {
+                                const float4 v = __ldcg(ps + static_cast<size_t>(h * 16 + j) * 128);
                                 sum[4 * j + 0] += v.x;
                                 sum[4 * j + 1] += v.y;
                                 sum[4 * j + 2] += v.z;
                                 sum[4 * j + 3] += v.w;
                             }
                         }
-                        if (mvalid) {
-                            __nv_bfloat16* crow = p.C + static_cast<size_t>(m) * p.N + ncol0 + c * 32;
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                if (ncol0 + c * 32 + j * 8 < p.N) {
-                                    uint4 q;
-                                    q.x = pack_bf16x2(sum[j * 8 + 0], sum[j * 8 + 1]);
-                                    q.y = pack_bf16x2(sum[j * 8 + 2], sum[j * 8 + 3]);
-                                    q.z = pack_bf16x2(sum[j * 8 + 4], sum[j * 8 + 5]);
-                                    q.w = pack_bf16x2(sum[j * 8 + 6], sum[j * 8 + 7]);
-                                    *reinterpret_cast<uint4*>(crow + j * 8) = q;
-                                }
-                            }
-                        }
+                        stage_and_store_64(&tmC, my_stg, my_stg_addr, lane, FloatCols{sum}, ncol0 + h * 64, m0 + quarter * 32, p.M, p.N);
                     }
                 }
             }
+#ifdef FP8BS_PROFILE
+            t_epi += clock64() - epi_start;
+#endif
         }
+#ifdef FP8BS_PROFILE
+        t_epi += 0;
+        if (pw == 0 && lane == 0) { PROF_OUT(4, w_sfull); PROF_OUT(5, w_tfull); PROF_OUT(6, t_fma); PROF_OUT(7, t_epi); PROF_STAMP(13); }
+#endif
+        // C must have been read out of shared memory before the CTA goes away
+        if (lane == 0) ptx::tma_store_wait_read<0>();
+        __syncwarp();
     }
 
     // ---------------------------------------------------------------- common exit -----
     ptx::tc_fence_before_sync();
     __syncthreads();
+    if constexpr (CG == 2) ptx::cluster_sync();      // nothing remote may touch this CTA after it has left
     if (warp == 1) {
         __syncwarp();
         ptx::tc_fence_after_sync();
-        ptx::tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+        if constexpr (CG == 2) ptx::tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
+        else ptx::tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
     }
+    if (threadIdx.x == 0) { PROF_STAMP(14); }
 }
 
 }  // namespace fp8bs

@@ -162,6 +162,206 @@ __device__ __forceinline__ void tmem_ld_wait()
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+
+// ---------------------------------------------------------------- clusters ----------
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Address of the same shared-memory location in CTA `rank` of this cluster (shared::cluster window).
+__device__ __forceinline__ uint32_t mapa(uint32_t addr, uint32_t rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Arrive on an mbarrier that may live in another CTA of the cluster (shared::cluster address).
+// Default semantics on purpose: a cluster-scope release costs several hundred cycles per arrive, and the
+// TMEM hand-offs this is used for are ordered by tcgen05.fence::before_thread_sync / after_thread_sync.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
+{
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// TMA load issued by either CTA of a pair; the byte count is reported to `bar`, which may be the
+// peer CTA's barrier (shared::cluster address).  No multicast: the data lands in this CTA only.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* tm, int c0, int c1,
+                                                 uint32_t bar_cluster_addr)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tm)), "r"(c0), "r"(c1), "r"(bar_cluster_addr)
+        : "memory");
+}
+// cta_group::2 forms: TMEM is allocated in both CTAs of the pair at the same column address; the MMA
+// is issued by the leader CTA and reads A rows / B columns from both CTAs' shared memory.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t slot, uint32_t ncols)
+{
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair()
+{
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols)
+{
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void mma_f8f6f4_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrive on `bar` (shared::cluster address, this CTA's or the peer's) once the pair's MMAs issued so far are done.
+__device__ __forceinline__ void mma_commit_pair(uint32_t bar_cluster_addr)
+{
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 ::"r"(bar_cluster_addr)
+                 : "memory");
+}
+
+// ---------------------------------------------------------------- registers ---------
+template <int N>
+__device__ __forceinline__ void setmaxnreg_inc()
+{
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void setmaxnreg_dec()
+{
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+// ---------------------------------------------------------------- promotion ---------
+// acc[0..15] += sc * cur[0..31] (two columns per instruction).
+__device__ __forceinline__ void fma32(unsigned long long (&acc)[16], const uint32_t (&cur)[32], unsigned long long sc2)
+{
+    asm volatile(
+        "{\n\t.reg .b64 t;\n\t"
+        "mov.b64 t, {%16, %17};\n\tfma.rn.f32x2 %0, t, %48, %0;\n\t"
+        "mov.b64 t, {%18, %19};\n\tfma.rn.f32x2 %1, t, %48, %1;\n\t"
+        "mov.b64 t, {%20, %21};\n\tfma.rn.f32x2 %2, t, %48, %2;\n\t"
+        "mov.b64 t, {%22, %23};\n\tfma.rn.f32x2 %3, t, %48, %3;\n\t"
+        "mov.b64 t, {%24, %25};\n\tfma.rn.f32x2 %4, t, %48, %4;\n\t"
+        "mov.b64 t, {%26, %27};\n\tfma.rn.f32x2 %5, t, %48, %5;\n\t"
+        "mov.b64 t, {%28, %29};\n\tfma.rn.f32x2 %6, t, %48, %6;\n\t"
+        "mov.b64 t, {%30, %31};\n\tfma.rn.f32x2 %7, t, %48, %7;\n\t"
+        "mov.b64 t, {%32, %33};\n\tfma.rn.f32x2 %8, t, %48, %8;\n\t"
+        "mov.b64 t, {%34, %35};\n\tfma.rn.f32x2 %9, t, %48, %9;\n\t"
+        "mov.b64 t, {%36, %37};\n\tfma.rn.f32x2 %10, t, %48, %10;\n\t"
+        "mov.b64 t, {%38, %39};\n\tfma.rn.f32x2 %11, t, %48, %11;\n\t"
+        "mov.b64 t, {%40, %41};\n\tfma.rn.f32x2 %12, t, %48, %12;\n\t"
+        "mov.b64 t, {%42, %43};\n\tfma.rn.f32x2 %13, t, %48, %13;\n\t"
+        "mov.b64 t, {%44, %45};\n\tfma.rn.f32x2 %14, t, %48, %14;\n\t"
+        "mov.b64 t, {%46, %47};\n\tfma.rn.f32x2 %15, t, %48, %15;\n\t"
+        "}"
+        : "+l"(acc[0]), "+l"(acc[1]), "+l"(acc[2]), "+l"(acc[3]), "+l"(acc[4]), "+l"(acc[5]), "+l"(acc[6]), "+l"(acc[7]), "+l"(acc[8]), "+l"(acc[9]), "+l"(acc[10]), "+l"(acc[11]), "+l"(acc[12]), "+l"(acc[13]), "+l"(acc[14]), "+l"(acc[15])
+        : "r"(cur[0]), "r"(cur[1]), "r"(cur[2]), "r"(cur[3]), "r"(cur[4]), "r"(cur[5]), "r"(cur[6]), "r"(cur[7]), "r"(cur[8]), "r"(cur[9]), "r"(cur[10]), "r"(cur[11]), "r"(cur[12]), "r"(cur[13]), "r"(cur[14]), "r"(cur[15]), "r"(cur[16]), "r"(cur[17]), "r"(cur[18]), "r"(cur[19]), "r"(cur[20]), "r"(cur[21]), "r"(cur[22]), "r"(cur[23]), "r"(cur[24]), "r"(cur[25]), "r"(cur[26]), "r"(cur[27]), "r"(cur[28]), "r"(cur[29]), "r"(cur[30]), "r"(cur[31]), "l"(sc2));
+}
+// 32 columns from TMEM, complete on return (load and wait in one statement).
+__device__ __forceinline__ void tmem_ld_x32_sync(uint32_t taddr, uint32_t (&v)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n\t"
+        "tcgen05.wait::ld.sync.aligned;"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+
+// acc[0..15] += sc * cur[0..31] (two columns per instruction), cur being a 64-column buffer.
+__device__ __forceinline__ void fma32_from64_0(unsigned long long (&acc)[16], const uint32_t (&cur)[64], unsigned long long sc2)
+{
+    asm volatile(
+        "{\n\t.reg .b64 t;\n\t"
+        "mov.b64 t, {%16, %17};\n\tfma.rn.f32x2 %0, t, %48, %0;\n\t"
+        "mov.b64 t, {%18, %19};\n\tfma.rn.f32x2 %1, t, %48, %1;\n\t"
+        "mov.b64 t, {%20, %21};\n\tfma.rn.f32x2 %2, t, %48, %2;\n\t"
+        "mov.b64 t, {%22, %23};\n\tfma.rn.f32x2 %3, t, %48, %3;\n\t"
+        "mov.b64 t, {%24, %25};\n\tfma.rn.f32x2 %4, t, %48, %4;\n\t"
+        "mov.b64 t, {%26, %27};\n\tfma.rn.f32x2 %5, t, %48, %5;\n\t"
+        "mov.b64 t, {%28, %29};\n\tfma.rn.f32x2 %6, t, %48, %6;\n\t"
+        "mov.b64 t, {%30, %31};\n\tfma.rn.f32x2 %7, t, %48, %7;\n\t"
+        "mov.b64 t, {%32, %33};\n\tfma.rn.f32x2 %8, t, %48, %8;\n\t"
+        "mov.b64 t, {%34, %35};\n\tfma.rn.f32x2 %9, t, %48, %9;\n\t"
+        "mov.b64 t, {%36, %37};\n\tfma.rn.f32x2 %10, t, %48, %10;\n\t"
+        "mov.b64 t, {%38, %39};\n\tfma.rn.f32x2 %11, t, %48, %11;\n\t"
+        "mov.b64 t, {%40, %41};\n\tfma.rn.f32x2 %12, t, %48, %12;\n\t"
+        "mov.b64 t, {%42, %43};\n\tfma.rn.f32x2 %13, t, %48, %13;\n\t"
+        "mov.b64 t, {%44, %45};\n\tfma.rn.f32x2 %14, t, %48, %14;\n\t"
+        "mov.b64 t, {%46, %47};\n\tfma.rn.f32x2 %15, t, %48, %15;\n\t"
+        "}"
+        : "+l"(acc[0]), "+l"(acc[1]), "+l"(acc[2]), "+l"(acc[3]), "+l"(acc[4]), "+l"(acc[5]), "+l"(acc[6]), "+l"(acc[7]), "+l"(acc[8]), "+l"(acc[9]), "+l"(acc[10]), "+l"(acc[11]), "+l"(acc[12]), "+l"(acc[13]), "+l"(acc[14]), "+l"(acc[15])
+        : "r"(cur[0]), "r"(cur[1]), "r"(cur[2]), "r"(cur[3]), "r"(cur[4]), "r"(cur[5]), "r"(cur[6]), "r"(cur[7]), "r"(cur[8]), "r"(cur[9]), "r"(cur[10]), "r"(cur[11]), "r"(cur[12]), "r"(cur[13]), "r"(cur[14]), "r"(cur[15]), "r"(cur[16]), "r"(cur[17]), "r"(cur[18]), "r"(cur[19]), "r"(cur[20]), "r"(cur[21]), "r"(cur[22]), "r"(cur[23]), "r"(cur[24]), "r"(cur[25]), "r"(cur[26]), "r"(cur[27]), "r"(cur[28]), "r"(cur[29]), "r"(cur[30]), "r"(cur[31]), "l"(sc2));
+}
+
+// acc[0..15] += sc * cur[32..63] (two columns per instruction), cur being a 64-column buffer.
+__device__ __forceinline__ void fma32_from64_32(unsigned long long (&acc)[16], const uint32_t (&cur)[64], unsigned long long sc2)
+{
+    asm volatile(
+        "{\n\t.reg .b64 t;\n\t"
+        "mov.b64 t, {%16, %17};\n\tfma.rn.f32x2 %0, t, %48, %0;\n\t"
+        "mov.b64 t, {%18, %19};\n\tfma.rn.f32x2 %1, t, %48, %1;\n\t"
+        "mov.b64 t, {%20, %21};\n\tfma.rn.f32x2 %2, t, %48, %2;\n\t"
+        "mov.b64 t, {%22, %23};\n\tfma.rn.f32x2 %3, t, %48, %3;\n\t"
+        "mov.b64 t, {%24, %25};\n\tfma.rn.f32x2 %4, t, %48, %4;\n\t"
+        "mov.b64 t, {%26, %27};\n\tfma.rn.f32x2 %5, t, %48, %5;\n\t"
+        "mov.b64 t, {%28, %29};\n\tfma.rn.f32x2 %6, t, %48, %6;\n\t"
+        "mov.b64 t, {%30, %31};\n\tfma.rn.f32x2 %7, t, %48, %7;\n\t"
+        "mov.b64 t, {%32, %33};\n\tfma.rn.f32x2 %8, t, %48, %8;\n\t"
+        "mov.b64 t, {%34, %35};\n\tfma.rn.f32x2 %9, t, %48, %9;\n\t"
+        "mov.b64 t, {%36, %37};\n\tfma.rn.f32x2 %10, t, %48, %10;\n\t"
+        "mov.b64 t, {%38, %39};\n\tfma.rn.f32x2 %11, t, %48, %11;\n\t"
+        "mov.b64 t, {%40, %41};\n\tfma.rn.f32x2 %12, t, %48, %12;\n\t"
+        "mov.b64 t, {%42, %43};\n\tfma.rn.f32x2 %13, t, %48, %13;\n\t"
+        "mov.b64 t, {%44, %45};\n\tfma.rn.f32x2 %14, t, %48, %14;\n\t"
+        "mov.b64 t, {%46, %47};\n\tfma.rn.f32x2 %15, t, %48, %15;\n\t"
+        "}"
+        : "+l"(acc[0]), "+l"(acc[1]), "+l"(acc[2]), "+l"(acc[3]), "+l"(acc[4]), "+l"(acc[5]), "+l"(acc[6]), "+l"(acc[7]), "+l"(acc[8]), "+l"(acc[9]), "+l"(acc[10]), "+l"(acc[11]), "+l"(acc[12]), "+l"(acc[13]), "+l"(acc[14]), "+l"(acc[15])
+        : "r"(cur[32]), "r"(cur[33]), "r"(cur[34]), "r"(cur[35]), "r"(cur[36]), "r"(cur[37]), "r"(cur[38]), "r"(cur[39]), "r"(cur[40]), "r"(cur[41]), "r"(cur[42]), "r"(cur[43]), "r"(cur[44]), "r"(cur[45]), "r"(cur[46]), "r"(cur[47]), "r"(cur[48]), "r"(cur[49]), "r"(cur[50]), "r"(cur[51]), "r"(cur[52]), "r"(cur[53]), "r"(cur[54]), "r"(cur[55]), "r"(cur[56]), "r"(cur[57]), "r"(cur[58]), "r"(cur[59]), "r"(cur[60]), "r"(cur[61]), "r"(cur[62]), "r"(cur[63]), "l"(sc2));
+}
+
+
+// 64 columns from TMEM, complete on return (load and wait in one statement).
+__device__ __forceinline__ void tmem_ld_x64_sync(uint32_t taddr, uint32_t (&v)[64])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x64.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];\n\t"
+        "tcgen05.wait::ld.sync.aligned;"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31]), "=r"(v[32]), "=r"(v[33]), "=r"(v[34]), "=r"(v[35]), "=r"(v[36]), "=r"(v[37]), "=r"(v[38]), "=r"(v[39]), "=r"(v[40]), "=r"(v[41]), "=r"(v[42]), "=r"(v[43]), "=r"(v[44]), "=r"(v[45]), "=r"(v[46]), "=r"(v[47]), "=r"(v[48]), "=r"(v[49]), "=r"(v[50]), "=r"(v[51]), "=r"(v[52]), "=r"(v[53]), "=r"(v[54]), "=r"(v[55]), "=r"(v[56]), "=r"(v[57]), "=r"(v[58]), "=r"(v[59]), "=r"(v[60]), "=r"(v[61]), "=r"(v[62]), "=r"(v[63])
+        : "r"(taddr)
+        : "memory");
+}
+
 // ---------------------------------------------------------------- descriptors -------
 // Shared-memory matrix descriptor for an MN-major 8-bit operand held as rows of 128 bytes
 // (128 consecutive m or n) per k, 128-byte swizzled -- exactly what a TMA box

@@ -23,7 +23,8 @@
  *
  * Every function returns 0 on success or a negative FP8BS_ERR_* code; nothing throws or
  * aborts.  Requirements: M, N, K > 0; K % 128 == 0 (mn_large.hip:17); M % 16 == 0 and
- * N % 16 == 0 (16-byte strides of the column-major operands); A, B, C 16-byte aligned.
+ * N % 16 == 0 (16-byte strides of the column-major operands); A, B, C and a_scale
+ * 16-byte aligned.
  */
 #ifndef FP8BS_H
 #define FP8BS_H
@@ -50,6 +51,10 @@ extern "C" {
 #define FP8BS_PATH_MN_LARGE  1   /* persistent full-K kernel   (role of mn_large.hip) */
 #define FP8BS_PATH_MN_SMALL  2   /* split-K kernel             (role of mn_small.hip) */
 
+/* tile_n values: 0 = let the library choose; 128 or 256 = tile width with one CTA per 128-row tile;
+ * 256 | FP8BS_TILE_PAIR = a 256 x 256 tile owned by a pair of CTAs (tcgen05 cta_group::2). */
+#define FP8BS_TILE_PAIR      0x1000
+
 /* ---- the operator ---------------------------------------------------------------- */
 
 /* Run-time shape dispatch between the two kernels.  Replaces the reference's manual,
@@ -74,7 +79,7 @@ int fp8bs_gemm_mn_small(const void* A, const void* B, const float* a_scale, cons
 /* Everything explicit.  For an N-shard of a wider problem (multi-GPU partition by columns):
  * B and C hold columns [n0, n0+N) of an n_total-column problem, b_scale is the FULL
  * [ceil(n_total/128), K/128] array, n0 % 64 == 0.  The plain operator is n0 = 0,
- * n_total = N.  path: FP8BS_PATH_*; splits: 0 = choose; tile_n: 0 = choose, 128 or 256.
+ * n_total = N.  path: FP8BS_PATH_*; splits: 0 = choose; tile_n: see FP8BS_TILE_PAIR above.
  * No counterpart in the reference (it has no multi-GPU code); the arithmetic per element is
  * check.cu:38-48 with cy replaced by n0 + cy in the b_scale index. */
 int fp8bs_gemm_ex(const void* A, const void* B, const float* a_scale, const float* b_scale, void* C,
@@ -130,7 +135,8 @@ int fp8bs_host_ctx_destroy(fp8bs_host_ctx* ctx);
 /* Pinned staging buffers of the context (valid until destroy): fill these, then call. */
 void* fp8bs_host_ctx_buffer(fp8bs_host_ctx* ctx, int which); /* 0 A, 1 B, 2 a_scale, 3 b_scale, 4 C */
 int fp8bs_gemm_host(fp8bs_host_ctx* ctx, uint16_t* C, const void* A, const void* B,
-                    const float* a_scale, const float* b_scale, int M, int N, int K);
+                    const float* a_scale, const float* b_scale, int M, int N, int K, int n0,
+                    int n_total);
 
 /* Seeded synthetic inputs (role of genMat, utils.h:25-33, but counter-based so that any
  * slice can be generated independently).  Elements: N(0,1) rounded to nearest-even e4m3fn,
