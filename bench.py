@@ -13,7 +13,7 @@ the GEMM path), and a shape's time is the max over ranks.  Rank 0 prints ONE JSO
              distinct buffer sets to exceed twice the L2 (so every launch reads its operands from HBM)
   e2e        the same geomean through the host-buffer entry point fp8bs_gemm_host: H2D of A, B and
              both scale arrays from pinned memory, the GEMM, D2H of C, inside the timed region
-  roofline   the dominant kernel (full-K, tile 128x256) on M=6144 N=4608 K=7168 against the tensor peak
+  roofline   the dominant kernel (full-K, 256x256 CTA-pair tiles) on M=6144 N=4608 K=7168 against the tensor peak
   cpu_baseline  the reference's CPU path (dequantise -> gemmCPU of utils.h:65-76 -> bf16) when
              oracle/_ref is present, else the CPU restatement in oracle/, on a bounded row sample
   m16384     aggregate TFLOP/s on the M=16384 variants of the nine (N, K) pairs, same partition
@@ -76,7 +76,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -85,7 +85,11 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
+
+    def window(self, t0, t1):
+        """Keep only the samples taken between two wall-clock times (the timed region)."""
+        self.t0, self.t1 = t0, t1
 
     def stop(self):
         if self.proc is None:
@@ -97,7 +101,10 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons, power = [], [], set(), []
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        t0, t1 = getattr(self, "t0", 0.0), getattr(self, "t1", float("inf"))
+        for stamp, line in self.lines:
+            if not (t0 <= stamp <= t1 + 0.05):
+                continue
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 7:
                 continue
@@ -290,23 +297,24 @@ def run_gpu_arm(args, rank, world):
             if events is not None:
                 events[i][1].record()
 
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()            # started early: nvidia-smi needs a moment before its first sample
     for _ in range(max(args.warmup, 3)):
         one_step()
     barrier()
-
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in benches]
           for _ in range(args.steps)]
     launches_before = f.launch_count()
     barrier()
     t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    wall0 = time.time()
     t_start.record()
     for s in range(args.steps):
         one_step(ev[s])
     t_end.record()
     barrier()
+    sampler.window(wall0, time.time())
     clocks = sampler.stop() if rank == 0 else None
     # graph replays do not go through the library's launch counter: count the kernels they contain
     gpu_launches = args.steps * sum(b.launches_per_replay for b in benches) + (f.launch_count() - launches_before)
@@ -415,7 +423,8 @@ def run_gpu_arm(args, rank, world):
             traffic = json.load(fh).get("dram_bytes_per_launch")
     except Exception:
         pass
-    roofline = {"bound": "tensor", "kernel": "gemm_kernel<256,false> on M=6144 N=4608 K=7168 (1/%d column shard per GPU)" % world,
+    roofline = {"bound": "tensor", "kernel": "gemm_kernel<256,2,false> (256x256 CTA-pair tiles) on M=6144 N=4608 K=7168 "
+                                            "(1/%d column shard per GPU)" % world,
                 "achieved": round(dom_tflops, 1), "peak": round(fp8_peak, 1), "unit": "TFLOP/s",
                 "frac": round(dom_tflops / fp8_peak, 4),
                 "peak_source": "2 x bf16_tflops (burst) of %s: fp8 issues at twice the bf16 rate; of %s" %
@@ -450,7 +459,7 @@ def run_gpu_arm(args, rank, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     args = ap.parse_args()

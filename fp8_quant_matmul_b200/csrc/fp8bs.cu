@@ -27,6 +27,7 @@ static std::atomic<unsigned long long> g_launches{0};
 // Device status word written by kernels whose bounded waits expire.
 __device__ unsigned int g_device_status[4];
 
+
 #define CUDA_TRY(expr)                                     \
     do {                                                   \
         cudaError_t e__ = (expr);                          \
@@ -140,18 +141,25 @@ static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
 constexpr int SM_TARGET = 148;   // B200; the dispatch is a pure function of the shape
 
-// Estimated cost of a configuration in units of "one 128x128x128 block on one SM".
+// Estimated run time of a configuration in microseconds.  The constants come from a measured sweep of
+// every configuration over the 18 benchmark shapes on a B200 (power-capped, cold L2):
+//   per 128-K block of one work unit: 0.44 us (128-wide tile), 0.60 us (256-wide), 0.565 us (256 x 256 pair);
+//   per work unit (tile switch, epilogue): 0.35 / 0.9 / 1.6 us;  per launch: 3.5 us;
+//   split-K: 3.5 us + 1 us per split and 128 columns for the partial-sum round trip, doubled when a CTA has to
+//   walk more than one unit (the last-arriver reduction then delays the next unit).
 static double config_cost(int M, int N, int K, int tile_n, int splits, int cg)
 {
     const int KB = K / 128;
     const int tiles = ceil_div(M, 128 * cg) * ceil_div(N, tile_n);
     const int units = tiles * splits;
     const int waves = ceil_div(units, SM_TARGET / cg);
-    double per_kb = (tile_n == 256) ? 2.0 : 1.2;             // a 128-wide tile re-reads A twice as often
-    if (cg == 2) per_kb *= 0.9;                              // pairs fetch each B column once for 256 rows
-    const double per_unit = ceil_div(KB, splits) * per_kb + 4.0 * (tile_n / 128);   // + prologue/epilogue
-    double cost = waves * per_unit;
-    if (splits > 1) cost += 3.0 + 0.75 * splits;             // partial-sum round trip through L2
+    const double per_kb = (cg == 2) ? 0.565 : (tile_n == 256 ? 0.60 : 0.44);
+    const double per_unit = (cg == 2) ? 1.6 : (tile_n == 256 ? 0.9 : 0.35);
+    double cost = 3.5 + waves * (ceil_div(KB, splits) * per_kb + per_unit);
+    if (splits > 1) {
+        const double overhead = 3.5 + 1.0 * splits * (tile_n / 128);
+        cost += (waves > 1) ? 2.0 * overhead : overhead;
+    }
     return cost;
 }
 
