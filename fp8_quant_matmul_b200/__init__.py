@@ -16,6 +16,8 @@ from .api import (  # noqa: F401
     TILE_PAIR,
     gemm,
     gemm_ref,
+    gemm_mn_small_static,
+    STATIC_SCRATCH_BYTES,
     gemmGPU,
     HostContext,
     select_path,

@@ -33,6 +33,7 @@ _SIGS = {
     "fp8bs_gemm": (_c.c_int, [_c.c_void_p] * 5 + [_c.c_int] * 3 + [_c.c_void_p, _c.c_size_t, _c.c_void_p]),
     "fp8bs_gemm_mn_large": (_c.c_int, [_c.c_void_p] * 5 + [_c.c_int] * 3 + [_c.c_void_p]),
     "fp8bs_gemm_mn_small": (_c.c_int, [_c.c_void_p] * 5 + [_c.c_int] * 4 + [_c.c_void_p, _c.c_size_t, _c.c_void_p]),
+    "fp8bs_gemm_mn_small_static": (_c.c_int, [_c.c_void_p] * 5 + [_c.c_int] * 4 + [_c.c_void_p]),
     "fp8bs_gemm_ex": (_c.c_int, [_c.c_void_p] * 5 + [_c.c_int] * 8 + [_c.c_void_p, _c.c_size_t, _c.c_void_p]),
     "fp8bs_gemm_ref": (_c.c_int, [_c.c_void_p] * 5 + [_c.c_int] * 3 + [_c.c_void_p]),
     "fp8bs_select_path": (_c.c_int, [_c.c_int] * 3 + [_c.POINTER(_c.c_int)] * 2),
@@ -206,6 +207,25 @@ def gemm(A, B, a_scale, b_scale, C=None, M=None, N=None, K=None, path=PATH_AUTO,
     rc = lib().fp8bs_gemm_ex(A.data_ptr(), B.data_ptr(), a_scale.data_ptr(), b_scale.data_ptr(), C.data_ptr(),
                              M, N, K, n0, n_total, path, splits, tile_n, ws_ptr, ws_bytes, stream)
     _check(rc, "fp8bs_gemm_ex")
+    return C
+
+
+STATIC_SCRATCH_BYTES = (32 << 20) + 65536
+
+
+def gemm_mn_small_static(A, B, a_scale, b_scale, M, N, K, splits=0, C=None):
+    """Split-K GEMM on the library's built-in scratch array: nothing is allocated, no workspace is passed.
+
+    For callers that cannot allocate device memory when they call.  Problems whose partial sums exceed
+    STATIC_SCRATCH_BYTES raise Fp8bsError(-4).  Calls share the scratch: keep them ordered on the GPU.
+    C must be given if the caller truly cannot allocate; it is created here only as a convenience.
+    """
+    torch = _torch()
+    if C is None:
+        C = torch.empty((M, N), dtype=torch.bfloat16, device=A.device)
+    stream = torch.cuda.current_stream(A.device).cuda_stream
+    _check(lib().fp8bs_gemm_mn_small_static(A.data_ptr(), B.data_ptr(), a_scale.data_ptr(), b_scale.data_ptr(),
+                                            C.data_ptr(), M, N, K, splits, stream), "fp8bs_gemm_mn_small_static")
     return C
 
 

@@ -27,6 +27,11 @@ static std::atomic<unsigned long long> g_launches{0};
 // Device status word written by kernels whose bounded waits expire.
 __device__ unsigned int g_device_status[4];
 
+// Built-in split-K scratch for fp8bs_gemm_mn_small_static: tile counters (first 64 KiB) followed by the fp32
+// partial sums.  It lives in the library's device image, so every GPU that loads the library holds these
+// bytes until the process exits; that is why the size is kept modest.
+constexpr size_t STATIC_SCRATCH_BYTES = FP8BS_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_BYTES];
 
 #define CUDA_TRY(expr)                                     \
     do {                                                   \
@@ -48,6 +53,7 @@ struct DeviceInfo {
     int status = FP8BS_OK;
     int sm_count = 0;
     unsigned int* status_ptr = nullptr;            // device address of g_device_status
+    void* static_scratch = nullptr;                // device address of g_static_scratch (looked up on first use)
 };
 static DeviceInfo g_dev[MAX_DEVICES];
 static std::mutex g_dev_mutex;
@@ -513,6 +519,40 @@ int fp8bs_gemm_ex(const void* A, const void* B, const float* a_scale, const floa
 {
     return gemm_impl(A, B, a_scale, b_scale, C, M, N, K, n0, n_total, path, splits, tile_n, workspace,
                      workspace_bytes, stream);
+}
+
+// Split-K GEMM for callers that must not allocate.  The scratch is the file-scope device array above: in host code
+// its name is only a handle, so the real device address is fetched once per device with cudaGetSymbolAddress
+// (with that device current) and handed to the kernel like any caller-provided workspace.
+int fp8bs_gemm_mn_small_static(const void* A, const void* B, const float* a_scale, const float* b_scale, void* C,
+                               int M, int N, int K, int splits, void* stream)
+{
+    if (!A || !B || !a_scale || !b_scale || !C) return FP8BS_ERR_NULL;
+    int rc = check_args(M, N, K, 0, N, FP8BS_PATH_MN_SMALL, splits, 0);
+    if (rc) return rc;
+    // refuse anything the built-in scratch cannot hold, before touching the device
+    const Config cfg = choose_config(M, N, K, FP8BS_PATH_MN_SMALL, splits, 0);
+    if (config_workspace(M, N, cfg) > STATIC_SCRATCH_BYTES) return FP8BS_ERR_WORKSPACE;
+    DeviceInfo* dev = nullptr;
+    rc = device_setup(&dev);                       // first call on a device: attribute set-up, no allocation
+    if (rc) return rc;
+    {
+        std::lock_guard<std::mutex> lock(g_dev_mutex);
+        if (!dev->static_scratch) {
+            void* ptr = nullptr;
+            const cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+            if (e != cudaSuccess || !ptr) {
+                tl_last_cuda_error = static_cast<int>(e);
+                (void)cudaGetLastError();
+                return FP8BS_ERR_CUDA;
+            }
+            dev->static_scratch = ptr;
+        }
+    }
+    // The array keeps whatever the previous call left: the tile counters must start at zero.
+    CUDA_TRY(cudaMemsetAsync(dev->static_scratch, 0, COUNTER_BYTES, static_cast<cudaStream_t>(stream)));
+    return gemm_impl(A, B, a_scale, b_scale, C, M, N, K, 0, N, FP8BS_PATH_MN_SMALL, splits, 0, dev->static_scratch,
+                     STATIC_SCRATCH_BYTES, stream);
 }
 
 int fp8bs_gemm_ref(const void* A, const void* B, const float* a_scale, const float* b_scale, void* C, int M, int N,

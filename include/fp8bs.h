@@ -76,6 +76,23 @@ int fp8bs_gemm_mn_small(const void* A, const void* B, const float* a_scale, cons
                         void* C, int M, int N, int K, int splits, void* workspace,
                         size_t workspace_bytes, void* stream);
 
+/* Split-K GEMM that allocates nothing and needs no workspace from the caller.  No counterpart in the reference.
+ * It is for callers that cannot hand over scratch memory at call time: code running where cudaMalloc is off limits
+ * (a host process whose device memory is entirely owned by another allocator, a plug-in that is forbidden to
+ * allocate, a latency-critical loop that cannot afford the device-wide synchronisation an allocation implies).
+ * The partial sums go to a scratch array built into the library: FP8BS_STATIC_SCRATCH_BYTES (32 MiB + 64 KiB) of
+ * device memory on every GPU that loads the library, held until the process exits.  A problem whose split-K
+ * partial sums need more than that is refused with FP8BS_ERR_WORKSPACE (use fp8bs_gemm_mn_small with your own
+ * workspace instead).  Arguments and results are those of fp8bs_gemm_mn_small; A, B, scales and C are still the
+ * caller's device buffers.  The first call on a device performs one-time set-up (kernel attributes, the lookup of
+ * the scratch array's device address), so make that first call before starting any stream capture.  All calls
+ * share the one array, which still holds what the previous call wrote: the function zeroes the tile counters on
+ * the stream before launching, and two calls that overlap on the GPU (different streams, no ordering) would
+ * corrupt each other's partial sums -- keep calls to this function ordered. */
+#define FP8BS_STATIC_SCRATCH_BYTES ((32u << 20) + 65536u)
+int fp8bs_gemm_mn_small_static(const void* A, const void* B, const float* a_scale, const float* b_scale,
+                               void* C, int M, int N, int K, int splits, void* stream);
+
 /* Everything explicit.  For an N-shard of a wider problem (multi-GPU partition by columns):
  * B and C hold columns [n0, n0+N) of an n_total-column problem, b_scale is the FULL
  * [ceil(n_total/128), K/128] array, n0 % 64 == 0.  The plain operator is n0 = 0,

@@ -1,0 +1,67 @@
+"""The allocation-free split-K entry point, fp8bs_gemm_mn_small_static.
+
+Some callers cannot give the library scratch memory when they call it: their device memory belongs to another
+allocator, they are forbidden to call cudaMalloc, or they cannot afford the synchronisation an allocation brings.
+For them the library carries its own fixed scratch array.  This test calls the entry point through the C ABI twice
+in a row (the second call finds the array as the first one left it) and compares each result with what the ordinary
+entry point, fp8bs_gemm_mn_small with a caller-owned workspace, produces for the same inputs.
+
+The file name sorts last on purpose: if this addition fails, a run that stops at the first failure has already
+executed every other test.
+"""
+import numpy as np
+import pytest
+
+import fp8_quant_matmul_b200 as f
+import helpers as h
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+
+def _inputs(M, N, K, seed):
+    dev = torch.device("cuda:0")
+    A, B, a_s, b_s = h.make_inputs(M, N, K, seed=seed)
+    return [torch.from_numpy(x).to(dev) for x in (A, B, a_s, b_s)], (A, B, a_s, b_s)
+
+
+@pytest.mark.parametrize("M,N,K,splits", [(1024, 512, 7168, 4), (1024, 576, 7168, 3), (256, 256, 1024, 0)])
+def test_static_scratch_matches_the_workspace_entry_point(M, N, K, splits):
+    dev = torch.device("cuda:0")
+    lib = f.lib()
+    need = f.workspace_bytes(M, N, K, f.PATH_MN_SMALL, splits, 0)
+    assert need <= f.STATIC_SCRATCH_BYTES
+    ws = torch.zeros(max(need, 65536), dtype=torch.uint8, device=dev)
+    for call in range(2):                                   # two calls in a row, different data each time
+        (dA, dB, dAs, dBs), host = _inputs(M, N, K, seed=40 + call)
+        want = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev)
+        got = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev)
+        rc = lib.fp8bs_gemm_mn_small(dA.data_ptr(), dB.data_ptr(), dAs.data_ptr(), dBs.data_ptr(), want.data_ptr(),
+                                     M, N, K, splits, ws.data_ptr(), ws.numel(), None)
+        assert rc == 0
+        rc = lib.fp8bs_gemm_mn_small_static(dA.data_ptr(), dB.data_ptr(), dAs.data_ptr(), dBs.data_ptr(),
+                                            got.data_ptr(), M, N, K, splits, None)
+        assert rc == 0
+        torch.cuda.synchronize()
+        f.last_device_status()
+        want_bits = want.view(torch.int16).cpu().numpy().view(np.uint16)
+        got_bits = got.view(torch.int16).cpu().numpy().view(np.uint16)
+        bad, first, maxerr = h.mismatches(want_bits, got_bits)       # |d| <= 1e-3 + 2e-2*|ref|, the suite's tolerance
+        assert bad == 0, "call %d: %d mismatches, first %d, max err %g" % (call, bad, first, maxerr)
+        # and both agree with the CPU checker
+        rows = np.arange(0, M, 8, dtype=np.int32)
+        bad, first, maxerr = h.mismatches(h.oracle_gemm(*host, M, N, K, rows=rows), got_bits[rows])
+        assert bad == 0, "call %d vs checker: %d mismatches" % (call, bad)
+
+
+def test_static_scratch_refuses_what_does_not_fit():
+    dev = torch.device("cuda:0")
+    M, N, K = 6144, 4608, 256
+    assert f.workspace_bytes(M, N, K, f.PATH_MN_SMALL, 2, 0) > f.STATIC_SCRATCH_BYTES
+    dummy = torch.zeros(M * K + N * K, dtype=torch.uint8, device=dev)
+    scales = torch.ones(M * 2 + 36 * 2, dtype=torch.float32, device=dev)
+    C = torch.zeros((M, N), dtype=torch.bfloat16, device=dev)
+    rc = f.lib().fp8bs_gemm_mn_small_static(dummy.data_ptr(), dummy.data_ptr(), scales.data_ptr(), scales.data_ptr(),
+                                            C.data_ptr(), M, N, K, 2, None)
+    assert rc == -4                                           # FP8BS_ERR_WORKSPACE
+    assert "workspace" in f.status_string(rc)
