@@ -192,7 +192,7 @@ def run_reference_arm(args, rank):
             "config": {"workload": "18-shape sweep M in {1024,6144} x 9 (N,K) pairs, CPU path on a row sample"},
             "cpu_baseline": best,
             "e2e": {"value": best["value"], "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # ----------------------------------------------------------------------------- GPU arm -------
@@ -451,12 +451,34 @@ def run_gpu_arm(args, rank, world):
         "m16384": {"aggregate_tflops": round(agg_flops / agg_us / 1e6, 1), "per_shape": m16},
         "allgather_c": allgather,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
     if dist is not None:
         dist.destroy_process_group()
 
 
+_JSON_FD = None
+
+
+def _quiet_stdout():
+    """Route everything libraries print on file descriptor 1 (the NCCL banner, for one) to stderr, and keep the
+    original stdout for the single JSON line."""
+    global _JSON_FD
+    sys.stdout.flush()
+    _JSON_FD = os.dup(1)
+    os.dup2(2, 1)
+
+
+def emit(line):
+    data = (json.dumps(line) + "\n").encode()
+    if _JSON_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_JSON_FD, data)
+
+
 def main():
+    _quiet_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=30)
