@@ -14,11 +14,14 @@ from .api import (  # noqa: F401
     PATH_MN_LARGE,
     PATH_MN_SMALL,
     TILE_PAIR,
+    SPLIT_WORKSPACE,
     gemm,
     gemm_ref,
     gemm_mn_small_static,
     STATIC_SCRATCH_BYTES,
     gemmGPU,
+    quantize_rowwise,
+    quantize_block,
     HostContext,
     select_path,
     workspace_bytes,

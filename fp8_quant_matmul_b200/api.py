@@ -13,6 +13,7 @@ _LIB_PATH = os.path.join(_PKG_DIR, "lib", "libfp8bs.so")
 
 PATH_AUTO, PATH_MN_LARGE, PATH_MN_SMALL = 0, 1, 2
 TILE_PAIR = 0x1000      # tile_n = 256 | TILE_PAIR: a 256 x 256 tile owned by a pair of CTAs
+SPLIT_WORKSPACE = 0x2000  # OR into tile_n: reduce split-K partial sums through the workspace, not in a cluster
 
 # The 18 benchmark shapes (M, N, K) of the reference's results table (README.md:15-25).
 SHAPES_18 = [(m, n, k) for m in (1024, 6144)
@@ -49,6 +50,8 @@ _SIGS = {
     "fp8bs_host_ctx_destroy": (_c.c_int, [_c.c_void_p]),
     "fp8bs_host_ctx_buffer": (_c.c_void_p, [_c.c_void_p, _c.c_int]),
     "fp8bs_gemm_host": (_c.c_int, [_c.c_void_p] * 6 + [_c.c_int] * 5),
+    "fp8bs_quantize_rowwise": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_float, _c.c_void_p]),
+    "fp8bs_quantize_block": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_float, _c.c_void_p]),
     "fp8bs_gen_normal_e4m3": (_c.c_int, [_c.c_void_p, _c.c_size_t, _c.c_uint64]),
     "fp8bs_gen_uniform_f32": (_c.c_int, [_c.c_void_p, _c.c_size_t, _c.c_uint64, _c.c_float, _c.c_float]),
     "fp8bs_float_to_e4m3fn": (_c.c_uint8, [_c.c_float]),
@@ -238,6 +241,35 @@ def gemm_ref(A, B, a_scale, b_scale, M, N, K, C=None):
     _check(lib().fp8bs_gemm_ref(A.data_ptr(), B.data_ptr(), a_scale.data_ptr(), b_scale.data_ptr(), C.data_ptr(),
                                 M, N, K, stream), "fp8bs_gemm_ref")
     return C
+
+
+def _quantize(fn_name, X, fp8_max):
+    torch = _torch()
+    if not X.is_cuda or X.dim() != 2 or not X.is_contiguous():
+        raise ValueError("expected a contiguous 2-D CUDA tensor [rows, K]")
+    if X.dtype not in (torch.float32, torch.bfloat16):
+        raise ValueError("fp32 or bf16 input")
+    rows, K = X.shape
+    q = torch.empty(rows * K, dtype=torch.uint8, device=X.device)
+    block = fn_name.endswith("block")
+    n_scales = (K // 128) * (((rows + 127) // 128) if block else rows)
+    scales = torch.empty(n_scales, dtype=torch.float32, device=X.device)
+    stream = torch.cuda.current_stream(X.device).cuda_stream
+    _check(getattr(lib(), fn_name)(X.data_ptr(), int(X.dtype == torch.bfloat16), q.data_ptr(), scales.data_ptr(),
+                                   rows, K, float(fp8_max), stream), fn_name)
+    return q, scales
+
+
+def quantize_rowwise(X, fp8_max=448.0):
+    """A and a_scale of the GEMM from a row-major [M, K] activation matrix (quantize.py:43-67).
+    Returns (A bytes column-major, flat; inverse scales laid out a_scale[m + M*kb])."""
+    return _quantize("fp8bs_quantize_rowwise", X, fp8_max)
+
+
+def quantize_block(W, fp8_max=448.0):
+    """B and b_scale of the GEMM from a row-major [N, K] weight matrix (128 x 128 blocks, quantize.py:16-41).
+    Returns (B bytes column-major, flat; inverse scales laid out b_scale[nb + ceil(N/128)*kb])."""
+    return _quantize("fp8bs_quantize_block", W, fp8_max)
 
 
 def last_device_status(stream=None):

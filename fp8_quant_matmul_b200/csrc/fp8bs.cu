@@ -63,17 +63,16 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
                                   CUtensorMapFloatOOBfill);
 static EncodeTiledFn g_encode_tiled = nullptr;
+static const bool g_use_pdl = []() { const char* e = std::getenv("FP8BS_PDL"); return !(e && e[0] == '0'); }();
 #ifdef FP8BS_PROFILE
 static long long* g_prof_buf = nullptr;
 #endif
 
-template <int BN, int CG, bool SPLITK>
+template <int BN, int CG, int MODE>
 static int prepare_kernel()
 {
-    CUDA_TRY(cudaFuncSetAttribute(gemm_kernel<BN, CG, SPLITK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    CUDA_TRY(cudaFuncSetAttribute(gemm_kernel<BN, CG, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   TileCfg<BN, CG>::SMEM_BYTES));
-    if (CG == 2)
-        CUDA_TRY(cudaFuncSetAttribute(gemm_kernel<BN, CG, SPLITK>, cudaFuncAttributeNonPortableClusterSizeAllowed, 0));
     return FP8BS_OK;
 }
 
@@ -109,9 +108,10 @@ static int device_setup(DeviceInfo** out)
             g_encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
         }
         int rc;
-        if ((rc = prepare_kernel<128, 1, false>()) || (rc = prepare_kernel<256, 1, false>()) ||
-            (rc = prepare_kernel<256, 2, false>()) || (rc = prepare_kernel<128, 1, true>()) ||
-            (rc = prepare_kernel<256, 1, true>()) || (rc = prepare_kernel<256, 2, true>())) {
+        if ((rc = prepare_kernel<128, 1, 0>()) || (rc = prepare_kernel<256, 1, 0>()) ||
+            (rc = prepare_kernel<256, 2, 0>()) || (rc = prepare_kernel<128, 1, 1>()) ||
+            (rc = prepare_kernel<256, 1, 1>()) || (rc = prepare_kernel<256, 2, 1>()) ||
+            (rc = prepare_kernel<128, 1, 2>()) || (rc = prepare_kernel<256, 1, 2>())) {
             d.status = rc;
             return rc;
         }
@@ -141,7 +141,10 @@ struct Config {
     int tile_n;   // 128 or 256
     int splits;   // 1 for mn_large
     int cg;       // 1: a CTA owns 128 rows of a tile; 2: a pair of CTAs owns 256 rows
+    int mode;     // 0 full K; 1 split-K reduced through a workspace; 2 split-K reduced inside a cluster
 };
+
+constexpr int MAX_CLUSTER_SPLITS = 6;   // clusters of 7 or 8 CTAs of this size fit only 15 at a time on a B200
 
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
@@ -151,18 +154,25 @@ constexpr int SM_TARGET = 148;   // B200; the dispatch is a pure function of the
 // every configuration over the 18 benchmark shapes on a B200 (power-capped, cold L2):
 //   per 128-K block of one work unit: 0.44 us (128-wide tile), 0.60 us (256-wide), 0.565 us (256 x 256 pair);
 //   per work unit (tile switch, epilogue): 0.35 / 0.9 / 1.6 us;  per launch: 3.5 us;
-//   split-K: 3.5 us + 1 us per split and 128 columns for the partial-sum round trip, doubled when a CTA has to
-//   walk more than one unit (the last-arriver reduction then delays the next unit).
-static double config_cost(int M, int N, int K, int tile_n, int splits, int cg)
+//   split-K through a workspace: 3.5 us + 1 us per split and 128 columns for the partial-sum round trip, doubled
+//   when a CTA has to walk more than one unit (the last-arriver reduction then delays the next unit);
+//   split-K inside a cluster: one CTA per (tile, K range); the number of clusters that fit on the GPU at once is
+//   cudaOccupancyMaxActiveClusters for this kernel's footprint (one CTA per SM), tabulated below for a B200;
+//   overhead 2 us (3 us for 256-wide tiles) + 0.5 us per split and 128 columns (shared-memory round trip, two
+//   cluster barriers).
+static const int kMaxActiveClusters[9] = {0, 148, 74, 45, 33, 26, 22, 15, 15};
+static double config_cost(int M, int N, int K, int tile_n, int splits, int cg, int mode)
 {
     const int KB = K / 128;
     const int tiles = ceil_div(M, 128 * cg) * ceil_div(N, tile_n);
     const int units = tiles * splits;
-    const int waves = ceil_div(units, SM_TARGET / cg);
+    const int waves = (mode == 2) ? ceil_div(tiles, kMaxActiveClusters[splits]) : ceil_div(units, SM_TARGET / cg);
     const double per_kb = (cg == 2) ? 0.565 : (tile_n == 256 ? 0.60 : 0.44);
     const double per_unit = (cg == 2) ? 1.6 : (tile_n == 256 ? 0.9 : 0.35);
     double cost = 3.5 + waves * (ceil_div(KB, splits) * per_kb + per_unit);
-    if (splits > 1) {
+    if (splits > 1 && mode == 2) {
+        cost += (tile_n == 256 ? 3.0 : 2.0) + 0.5 * splits * (tile_n / 128);
+    } else if (splits > 1) {
         const double overhead = 3.5 + 1.0 * splits * (tile_n / 128);
         cost += (waves > 1) ? 2.0 * overhead : overhead;
     }
@@ -170,24 +180,30 @@ static double config_cost(int M, int N, int K, int tile_n, int splits, int cg)
 }
 
 // tile_n argument of the API: 0 = choose; 128 or 256 = tile width, one CTA per tile;
-// 256 | FP8BS_TILE_PAIR = 256 x 256 tile owned by a pair of CTAs.
+// 256 | FP8BS_TILE_PAIR = 256 x 256 tile owned by a pair of CTAs; | FP8BS_SPLIT_WORKSPACE = reduce split-K partial
+// sums through the workspace even where the cluster reduction could be used.
 static Config choose_config(int M, int N, int K, int path, int splits, int tile_n)
 {
     const int KB = K / 128;
-    Config best{FP8BS_PATH_MN_LARGE, 128, 1, 1};
+    const bool force_ws = (tile_n & FP8BS_SPLIT_WORKSPACE) != 0;
+    const int want_tile = tile_n & ~FP8BS_SPLIT_WORKSPACE;
+    Config best{FP8BS_PATH_MN_LARGE, 128, 1, 1, 0};
     double best_cost = 1e300;
     for (int cg = 1; cg <= 2; ++cg)
         for (int tn = 128; tn <= 256; tn += 128) {
             if (cg == 2 && tn != 256) continue;
-            if (tile_n && tile_n != (tn | (cg == 2 ? FP8BS_TILE_PAIR : 0))) continue;
+            if (want_tile && want_tile != (tn | (cg == 2 ? FP8BS_TILE_PAIR : 0))) continue;
             const int smax = (path == FP8BS_PATH_MN_LARGE) ? 1 : (KB < MAX_SPLITS ? KB : MAX_SPLITS);
             for (int s = 1; s <= smax; ++s) {
                 if (splits && s != splits) continue;
-                const double c = config_cost(M, N, K, tn, s, cg);
-                if (c < best_cost) {
-                    best_cost = c;
-                    best = Config{(s > 1 || path == FP8BS_PATH_MN_SMALL) ? FP8BS_PATH_MN_SMALL : FP8BS_PATH_MN_LARGE,
-                                  tn, s, cg};
+                const bool small = (s > 1 || path == FP8BS_PATH_MN_SMALL);
+                const bool cluster_ok = small && cg == 1 && s >= 2 && s <= MAX_CLUSTER_SPLITS && !force_ws;
+                for (int mode = small ? 1 : 0; mode <= (cluster_ok ? 2 : (small ? 1 : 0)); ++mode) {
+                    const double c = config_cost(M, N, K, tn, s, cg, mode);
+                    if (c < best_cost) {
+                        best_cost = c;
+                        best = Config{small ? FP8BS_PATH_MN_SMALL : FP8BS_PATH_MN_LARGE, tn, s, cg, mode};
+                    }
                 }
             }
         }
@@ -196,7 +212,7 @@ static Config choose_config(int M, int N, int K, int path, int splits, int tile_
 
 static size_t config_workspace(int M, int N, const Config& c)
 {
-    if (c.path != FP8BS_PATH_MN_SMALL) return 0;
+    if (c.path != FP8BS_PATH_MN_SMALL || c.mode != 1) return 0;      // only the workspace reduction needs scratch
     const size_t half_tiles = static_cast<size_t>(ceil_div(M, 128 * c.cg)) * c.cg * ceil_div(N, c.tile_n);
     return COUNTER_BYTES + half_tiles * c.splits * (static_cast<size_t>(c.tile_n) * 128 * sizeof(float));
 }
@@ -215,7 +231,10 @@ static int check_args(int M, int N, int K, int n0, int n_total, int path, int sp
     if (path < FP8BS_PATH_AUTO || path > FP8BS_PATH_MN_SMALL) return FP8BS_ERR_ARG;
     if (splits < 0 || splits > K / 128 || splits > MAX_SPLITS) return FP8BS_ERR_ARG;
     if (path == FP8BS_PATH_MN_LARGE && splits > 1) return FP8BS_ERR_ARG;
-    if (tile_n != 0 && tile_n != 128 && tile_n != 256 && tile_n != (256 | FP8BS_TILE_PAIR)) return FP8BS_ERR_ARG;
+    {
+        const int t = tile_n & ~FP8BS_SPLIT_WORKSPACE;
+        if (t != 0 && t != 128 && t != 256 && t != (256 | FP8BS_TILE_PAIR)) return FP8BS_ERR_ARG;
+    }
     if (n0 < 0 || n0 % 64 != 0 || n_total < n0 + N) return FP8BS_ERR_ARG;
     return FP8BS_OK;
 }
@@ -279,36 +298,45 @@ struct TensorMaps {
     CUtensorMap A, B, As, C;
 };
 
-template <int BN, int CG, bool SPLITK>
+template <int BN, int CG, int MODE>
 static int launch(const TensorMaps& tm, const GemmParams& p, int sm_count, cudaStream_t stream)
 {
     using Cfg = TileCfg<BN, CG>;
     const int units = p.m_tiles * p.n_tiles * p.splits;
-    const int groups = units < sm_count / CG ? units : sm_count / CG;    // tile walkers: CTAs or CTA pairs
+    int groups = units < sm_count / CG ? units : sm_count / CG;    // tile walkers: CTAs or CTA pairs
+    if (MODE == 2) groups = units;                                  // one CTA per (tile, K range); a cluster per tile
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(groups * CG), 1, 1);
     cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
     cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = CG;
+    attr[0].val.clusterDim.x = (MODE == 2) ? static_cast<unsigned>(p.splits) : CG;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    // The kernel does its set-up, then waits for the previous kernel of the stream (griddepcontrol.wait) before it
+    // touches global memory: letting it start early hides launch latency and set-up behind that kernel's tail.
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_kernel<BN, CG, SPLITK>, tm.A, tm.B, tm.As, tm.C, p);
+    cfg.numAttrs = g_use_pdl ? 2 : 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_kernel<BN, CG, MODE>, tm.A, tm.B, tm.As, tm.C, p);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     CUDA_TRY(e);
     return FP8BS_OK;
 }
 
-template <bool SPLITK>
 static int launch_config(const Config& c, const TensorMaps& tm, const GemmParams& p, int sm_count, cudaStream_t st)
 {
-    if (c.cg == 2) return launch<256, 2, SPLITK>(tm, p, sm_count, st);
-    if (c.tile_n == 256) return launch<256, 1, SPLITK>(tm, p, sm_count, st);
-    return launch<128, 1, SPLITK>(tm, p, sm_count, st);
+    if (c.mode == 2)
+        return c.tile_n == 256 ? launch<256, 1, 2>(tm, p, sm_count, st) : launch<128, 1, 2>(tm, p, sm_count, st);
+    if (c.mode == 1) {
+        if (c.cg == 2) return launch<256, 2, 1>(tm, p, sm_count, st);
+        return c.tile_n == 256 ? launch<256, 1, 1>(tm, p, sm_count, st) : launch<128, 1, 1>(tm, p, sm_count, st);
+    }
+    if (c.cg == 2) return launch<256, 2, 0>(tm, p, sm_count, st);
+    return c.tile_n == 256 ? launch<256, 1, 0>(tm, p, sm_count, st) : launch<128, 1, 0>(tm, p, sm_count, st);
 }
 
 static int gemm_impl(const void* A, const void* B, const float* a_scale, const float* b_scale, void* C, int M,
@@ -323,7 +351,7 @@ static int gemm_impl(const void* A, const void* B, const float* a_scale, const f
     if ((reinterpret_cast<uintptr_t>(a_scale) & 15u) || (reinterpret_cast<uintptr_t>(b_scale) & 3u)) return FP8BS_ERR_ALIGN;
 
     Config cfg = choose_config(M, N, K, path, splits, tile_n);
-    if (cfg.path == FP8BS_PATH_MN_SMALL) {
+    if (cfg.mode == 1) {
         const size_t need = config_workspace(M, N, cfg);
         const size_t half_tiles = static_cast<size_t>(ceil_div(M, 128 * cfg.cg)) * cfg.cg * ceil_div(N, cfg.tile_n);
         const bool fits = workspace && workspace_bytes >= need && half_tiles <= COUNTER_BYTES / sizeof(unsigned int) &&
@@ -368,12 +396,11 @@ static int gemm_impl(const void* A, const void* B, const float* a_scale, const f
 #endif
     cudaStream_t st = static_cast<cudaStream_t>(stream);
 
-    if (cfg.path == FP8BS_PATH_MN_SMALL) {
+    if (cfg.mode == 1) {
         p.counters = static_cast<unsigned int*>(workspace);
         p.partials = reinterpret_cast<float4*>(static_cast<char*>(workspace) + COUNTER_BYTES);
-        return launch_config<true>(cfg, tm, p, dev->sm_count, st);
     }
-    return launch_config<false>(cfg, tm, p, dev->sm_count, st);
+    return launch_config(cfg, tm, p, dev->sm_count, st);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -447,6 +474,10 @@ __host__ __device__ inline uint8_t float_to_e4m3fn_rne(float x)
     if (be > 15u || (be == 15u && q == 7u)) return sign | 0x7E;
     return sign | static_cast<uint8_t>((be << 3) | q);
 }
+
+}  // namespace fp8bs
+#include "quantize.cuh"
+namespace fp8bs {
 
 __global__ void convert_float_to_e4m3fn_kernel(const float* __restrict__ in, uint8_t* __restrict__ out, size_t n)
 {
@@ -531,7 +562,7 @@ int fp8bs_gemm_mn_small_static(const void* A, const void* B, const float* a_scal
     int rc = check_args(M, N, K, 0, N, FP8BS_PATH_MN_SMALL, splits, 0);
     if (rc) return rc;
     // refuse anything the built-in scratch cannot hold, before touching the device
-    const Config cfg = choose_config(M, N, K, FP8BS_PATH_MN_SMALL, splits, 0);
+    const Config cfg = choose_config(M, N, K, FP8BS_PATH_MN_SMALL, splits, FP8BS_SPLIT_WORKSPACE);
     if (config_workspace(M, N, cfg) > STATIC_SCRATCH_BYTES) return FP8BS_ERR_WORKSPACE;
     DeviceInfo* dev = nullptr;
     rc = device_setup(&dev);                       // first call on a device: attribute set-up, no allocation
@@ -551,8 +582,8 @@ int fp8bs_gemm_mn_small_static(const void* A, const void* B, const float* a_scal
     }
     // The array keeps whatever the previous call left: the tile counters must start at zero.
     CUDA_TRY(cudaMemsetAsync(dev->static_scratch, 0, COUNTER_BYTES, static_cast<cudaStream_t>(stream)));
-    return gemm_impl(A, B, a_scale, b_scale, C, M, N, K, 0, N, FP8BS_PATH_MN_SMALL, splits, 0, dev->static_scratch,
-                     STATIC_SCRATCH_BYTES, stream);
+    return gemm_impl(A, B, a_scale, b_scale, C, M, N, K, 0, N, FP8BS_PATH_MN_SMALL, splits, FP8BS_SPLIT_WORKSPACE,
+                     dev->static_scratch, STATIC_SCRATCH_BYTES, stream);
 }
 
 int fp8bs_gemm_ref(const void* A, const void* B, const float* a_scale, const float* b_scale, void* C, int M, int N,
@@ -575,7 +606,7 @@ int fp8bs_select_path(int M, int N, int K, int* splits, int* tile_n)
     if (rc) return rc;
     const Config c = choose_config(M, N, K, FP8BS_PATH_AUTO, 0, 0);
     if (splits) *splits = c.splits;
-    if (tile_n) *tile_n = c.tile_n | (c.cg == 2 ? FP8BS_TILE_PAIR : 0);
+    if (tile_n) *tile_n = c.tile_n | (c.cg == 2 ? FP8BS_TILE_PAIR : 0) | (c.mode == 1 ? FP8BS_SPLIT_WORKSPACE : 0);
     return c.path;
 }
 
@@ -786,6 +817,47 @@ int fp8bs_gemm_host(fp8bs_host_ctx* ctx, uint16_t* C, const void* A, const void*
     CUDA_TRY(cudaMemcpyAsync(C, c->dC, static_cast<size_t>(M) * N * 2, cudaMemcpyDeviceToHost, c->stream));
     CUDA_TRY(cudaStreamSynchronize(c->stream));
     return FP8BS_OK;
+}
+
+// ---- device-side quantisers (quantize.py) ------------------------------------------------------
+static int quantize_impl(bool block, const void* X, int x_is_bf16, void* out, float* scale_out, int rows, int K,
+                         float fp8_max, void* stream)
+{
+    if (!X || !out || !scale_out) return FP8BS_ERR_NULL;
+    if (rows <= 0 || K <= 0 || K % 128 != 0) return FP8BS_ERR_SHAPE;
+    if (rows % 16 != 0) return FP8BS_ERR_ALIGN;
+    if ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(out)) & 15u) return FP8BS_ERR_ALIGN;
+    if (!(fp8_max > 0.0f) || fp8_max > 448.0f) return FP8BS_ERR_ARG;
+    DeviceInfo* dev = nullptr;
+    const int rc = device_setup(&dev);
+    if (rc) return rc;
+    const dim3 grid(ceil_div(rows, 128), K / 128), blk(256);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    uint8_t* o = static_cast<uint8_t*>(out);
+    if (x_is_bf16) {
+        const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(X);
+        if (block) quantize_kernel<true, __nv_bfloat16><<<grid, blk, 0, st>>>(x, o, scale_out, rows, K, fp8_max);
+        else quantize_kernel<false, __nv_bfloat16><<<grid, blk, 0, st>>>(x, o, scale_out, rows, K, fp8_max);
+    } else {
+        const float* x = static_cast<const float*>(X);
+        if (block) quantize_kernel<true, float><<<grid, blk, 0, st>>>(x, o, scale_out, rows, K, fp8_max);
+        else quantize_kernel<false, float><<<grid, blk, 0, st>>>(x, o, scale_out, rows, K, fp8_max);
+    }
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    CUDA_TRY(cudaGetLastError());
+    return FP8BS_OK;
+}
+
+int fp8bs_quantize_rowwise(const void* X, int x_is_bf16, void* A_out, float* a_scale_out, int M, int K, float fp8_max,
+                           void* stream)
+{
+    return quantize_impl(false, X, x_is_bf16, A_out, a_scale_out, M, K, fp8_max, stream);
+}
+
+int fp8bs_quantize_block(const void* W, int w_is_bf16, void* B_out, float* b_scale_out, int N, int K, float fp8_max,
+                         void* stream)
+{
+    return quantize_impl(true, W, w_is_bf16, B_out, b_scale_out, N, K, fp8_max, stream);
 }
 
 // ---- generators / conversions (host only) -------------------------------------------------

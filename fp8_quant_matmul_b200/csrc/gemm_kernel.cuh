@@ -9,12 +9,16 @@
 //           loads its own 128 rows of A and its own half of the B columns, the leader issues
 //           tcgen05.mma.cta_group::2 (M = 256) that reads both CTAs' shared memory, and each
 //           CTA's TMEM receives its own 128 rows.  Halves the B traffic per output element.
-//   SPLITK  false "mn_large": persistent CTAs walk tiles over the whole K
+//   MODE    0 "mn_large": persistent CTAs walk tiles over the whole K
 //                 (replaces in_smem_kernel, mn_large.hip:11-128);
-//           true  "mn_small": every tile is cut into `splits` K ranges, partial sums go to an
-//                 fp32 workspace and whoever finishes a tile last adds them in split order
-//                 0..S-1, so the result does not depend on timing (replaces k_large_kernel,
-//                 mn_small.hip:10-137, which instead shrinks the tile to get more blocks).
+//           1, 2 "mn_small": every tile is cut into `splits` K ranges and the partial sums are
+//                 added in split order 0..S-1, so the result does not depend on timing (replaces
+//                 k_large_kernel, mn_small.hip:10-137, which instead shrinks the tile to get more
+//                 blocks).  MODE 2 (S <= 8): the S CTAs of a tile form a thread-block cluster, each
+//                 leaves its fp32 partial tile in its own shared memory, and after a cluster barrier
+//                 every CTA reduces 128/S rows straight out of its peers' shared memory (DSMEM):
+//                 no workspace, no atomics.  MODE 1 (any S, also pair tiles): partial sums go to an
+//                 fp32 workspace and whoever finishes a tile last adds them.
 //
 // Warp roles (no __syncthreads in the main loop; registers are moved from the first warpgroup
 // to the promotion warps with setmaxnreg):
@@ -197,7 +201,7 @@ __device__ __forceinline__ void stage_and_store_64(const CUtensorMap* tmC, uint8
     }
 }
 
-template <int BN, int CG, bool SPLITK>
+template <int BN, int CG, int MODE>
 __global__ void __launch_bounds__(TileCfg<BN, CG>::THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmAs, const __grid_constant__ CUtensorMap tmC, const GemmParams p)
@@ -206,6 +210,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     constexpr int STAGES = Cfg::STAGES;
     constexpr int NBUF = Cfg::NBUF;
     constexpr int SRING = Cfg::SRING;
+    constexpr bool SPLITK = (MODE != 0);
+    static_assert(MODE != 2 || CG == 1, "the cluster reduction uses the cluster for the K splits");
+    // MODE 2: fp32 partial tile of this CTA, rows padded by 16 bytes so that a warp's 32 rows hit distinct banks
+    constexpr int PART_PITCH = BN * 4 + 16;
+    static_assert(MODE != 2 || 128 * PART_PITCH <= STAGES * Cfg::STAGE_BYTES, "partial tile must fit in the stage area");
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = ptx::smem_u32(smem_raw);
@@ -230,7 +239,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     if (threadIdx.x == 0) { PROF_STAMP(8); }
-    const uint32_t rank = (CG == 2) ? ptx::cluster_ctarank() : 0u;     // 0 = leader of the pair
+    const uint32_t rank = (CG == 2) ? ptx::cluster_ctarank() : 0u;     // 0 = leader of the pair (MODE 2: not used)
     const int group_id = blockIdx.x / CG;                               // which tile walker this CTA belongs to
     const int num_groups = gridDim.x / CG;
 
@@ -270,6 +279,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = ctrl[0];
     volatile uint32_t* abort_flag = &ctrl[1];
+    // Everything above (barriers, TMEM, descriptor prefetch) touched no global data, so it may overlap the tail of
+    // the previous kernel in the stream; from here on operands are read and C is written.
+    ptx::grid_dependency_wait();
+    ptx::grid_launch_dependents();
     if (threadIdx.x == 0) { PROF_STAMP(9); }
 
     const int KB = p.K / Cfg::BK;
@@ -513,6 +526,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 for (int h = 0; h < Cfg::COLS / 64; ++h)
                     stage_and_store_64(&tmC, my_stg, my_stg_addr, lane, PackedCols{acc[2 * h], acc[2 * h + 1]},
                                        ncol0 + h * 64, m0 + quarter * 32, p.M, p.N);
+            } else if constexpr (MODE == 2) {
+                // ---- split-K through the cluster: leave this K range's partial tile in shared memory ----
+                // The stage buffers are free: every MMA of this CTA has completed (the last TMEM buffer was full)
+                // and every load that was issued has been consumed.
+                if (ok) {
+                    float4* dst = reinterpret_cast<float4*>(aligned + row_in_tile * PART_PITCH + grp * Cfg::COLS * 4);
+#pragma unroll
+                    for (int j = 0; j < Cfg::COLS / 4; ++j)
+                        dst[j] = make_float4(f32x2_lo(acc[j / 8][(2 * j) % 16]), f32x2_hi(acc[j / 8][(2 * j) % 16]),
+                                             f32x2_lo(acc[j / 8][(2 * j + 1) % 16]), f32x2_hi(acc[j / 8][(2 * j + 1) % 16]));
+                }
             } else {
                 // ---- split-K: publish this K range's partial sums ----
                 // One 128-row half-tile per CTA.  Layout [half-tile][split][column quad][row]: a warp's
@@ -590,10 +614,46 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         __syncwarp();
     }
 
+    if constexpr (MODE == 2) {
+        // ------------------------------------------------------------ cluster reduction ---
+        __syncthreads();                 // this CTA's partial tile is complete ...
+        ptx::cluster_sync();             // ... and so are those of the other K ranges of the tile
+        if (warp >= 4 && *abort_flag == 0u) {
+            const int S = p.splits;
+            const int my = static_cast<int>(ptx::cluster_ctarank());     // = this CTA's split index
+            int tile, m0, n0, kb0, kb1;
+            decode(static_cast<int>(blockIdx.x), tile, m0, n0, kb0, kb1);
+            const int r0 = (128 * my) / S, r1 = (128 * (my + 1)) / S;     // the rows this CTA finishes
+            uint32_t peer[8];
+#pragma unroll
+            for (int s = 0; s < 8; ++s) peer[s] = ptx::mapa(stage_base, static_cast<uint32_t>(s < S ? s : 0));
+            const int items = (r1 - r0) * (BN / 4);
+            for (int idx = static_cast<int>(threadIdx.x) - 128; idx < items; idx += Cfg::PROMO_THREADS) {
+                const int row = r0 + idx / (BN / 4), c4 = idx % (BN / 4);
+                const uint32_t off = static_cast<uint32_t>(row * PART_PITCH + c4 * 16);
+                float4 v[8];
+#pragma unroll
+                for (int s = 0; s < 8; ++s)
+                    if (s < S) v[s] = ptx::ld_shared_cluster_v4(peer[s] + off);
+                float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+                for (int s = 0; s < 8; ++s)              // fixed order 0, 1, .., S-1: bit-deterministic
+                    if (s < S) { sum.x += v[s].x; sum.y += v[s].y; sum.z += v[s].z; sum.w += v[s].w; }
+                const int m = m0 + row, n = n0 + c4 * 4;
+                if (m < p.M && n < p.N) {
+                    uint2 q;
+                    q.x = pack_bf16x2(sum.x, sum.y);
+                    q.y = pack_bf16x2(sum.z, sum.w);
+                    *reinterpret_cast<uint2*>(p.C + static_cast<size_t>(m) * p.N + n) = q;
+                }
+            }
+        }
+    }
+
     // ---------------------------------------------------------------- common exit -----
     ptx::tc_fence_before_sync();
     __syncthreads();
-    if constexpr (CG == 2) ptx::cluster_sync();      // nothing remote may touch this CTA after it has left
+    if constexpr (CG == 2 || MODE == 2) ptx::cluster_sync();   // nothing remote may touch this CTA after it has left
     if (warp == 1) {
         __syncwarp();
         ptx::tc_fence_after_sync();

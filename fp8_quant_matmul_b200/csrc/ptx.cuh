@@ -181,6 +181,16 @@ __device__ __forceinline__ void cluster_sync()
 {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// 16 bytes from the shared memory of any CTA of the cluster (address from mapa).
+__device__ __forceinline__ float4 ld_shared_cluster_v4(uint32_t cluster_addr)
+{
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "r"(cluster_addr)
+                 : "memory");
+    return v;
+}
 // Arrive on an mbarrier that may live in another CTA of the cluster (shared::cluster address).
 // Default semantics on purpose: a cluster-scope release costs several hundred cycles per arrive, and the
 // TMEM hand-offs this is used for are ordered by tcgen05.fence::before_thread_sync / after_thread_sync.
@@ -242,6 +252,20 @@ __device__ __forceinline__ void mma_commit_pair(uint32_t bar_cluster_addr)
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];"
                  ::"r"(bar_cluster_addr)
                  : "memory");
+}
+
+// ---------------------------------------------------------------- dependent launch --
+// Programmatic dependent launch: a kernel launched with the programmatic-stream-serialization attribute may start
+// while the kernel before it in the stream is still finishing.  grid_dependency_wait() blocks until that earlier
+// kernel has completed and its memory is visible; everything before it must not touch global memory.
+__device__ __forceinline__ void grid_dependency_wait()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+// Lets the next kernel in the stream (if it was launched as a programmatic dependent) begin its own prologue.
+__device__ __forceinline__ void grid_launch_dependents()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
 // ---------------------------------------------------------------- registers ---------

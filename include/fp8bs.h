@@ -54,6 +54,10 @@ extern "C" {
 /* tile_n values: 0 = let the library choose; 128 or 256 = tile width with one CTA per 128-row tile;
  * 256 | FP8BS_TILE_PAIR = a 256 x 256 tile owned by a pair of CTAs (tcgen05 cta_group::2). */
 #define FP8BS_TILE_PAIR      0x1000
+/* Split-K partial sums are normally reduced inside a thread-block cluster through shared memory (2..8 splits, one
+ * CTA per tile): no workspace is needed then.  OR this flag into tile_n to reduce through the workspace instead
+ * (always used for more than 8 splits and for pair tiles). */
+#define FP8BS_SPLIT_WORKSPACE 0x2000
 
 /* ---- the operator ---------------------------------------------------------------- */
 
@@ -71,7 +75,8 @@ int fp8bs_gemm_mn_large(const void* A, const void* B, const float* a_scale, cons
 
 /* Forced small-M.N / large-K path: replaces k_large_kernel<<<grid, block>>> (mn_small.hip:10;
  * launch at check.cu:92-101).  splits = 0 lets the library choose; 1 <= splits <= K/128.
- * Partial sums are added in split order, so repeated calls give bit-identical C. */
+ * Partial sums are added in split order, so repeated calls give bit-identical C.  The workspace is only used
+ * where fp8bs_workspace_bytes_ex reports a non-zero size for the configuration (may be NULL otherwise). */
 int fp8bs_gemm_mn_small(const void* A, const void* B, const float* a_scale, const float* b_scale,
                         void* C, int M, int N, int K, int splits, void* workspace,
                         size_t workspace_bytes, void* stream);
@@ -154,6 +159,20 @@ void* fp8bs_host_ctx_buffer(fp8bs_host_ctx* ctx, int which); /* 0 A, 1 B, 2 a_sc
 int fp8bs_gemm_host(fp8bs_host_ctx* ctx, uint16_t* C, const void* A, const void* B,
                     const float* a_scale, const float* b_scale, int M, int N, int K, int n0,
                     int n_total);
+
+/* Device-side quantisers that produce the GEMM's operands, following the reference's quantize.py.
+ * fp8bs_quantize_rowwise = to_float8_rowwise_scale (quantize.py:43-67): X is row-major [M, K] on the device (fp32, or
+ * bf16 when x_is_bf16 != 0, widened to fp32 first); one scale per (row, 128-K block): scale = fp8_max / max(|x|, 1e-12),
+ * q = e4m3fn(clamp(x * scale)).  Writes A_out column-major (A[m + M*k]) and the INVERSE scales a_scale_out[m + M*kb],
+ * i.e. the GEMM's A and a_scale.  fp8bs_quantize_block = to_float8_block_scale (quantize.py:16-41): W row-major [N, K],
+ * one scale per 128 x 128 block; writes B_out column-major (B[n + N*k]) and b_scale_out[nb + ceil(N/128)*kb].  Unlike
+ * the reference, N need not be a multiple of 128 (the last block is partial).  fp8_max is the largest magnitude to
+ * produce: 448 for the full e4m3fn range, 240 to stay within the values e4m3fnuz (the reference's default dtype) also has.
+ * M, N multiples of 16; K a multiple of 128; X/W and the outputs 16-byte aligned.  Asynchronous on `stream`. */
+int fp8bs_quantize_rowwise(const void* X, int x_is_bf16, void* A_out, float* a_scale_out, int M, int K,
+                           float fp8_max, void* stream);
+int fp8bs_quantize_block(const void* W, int w_is_bf16, void* B_out, float* b_scale_out, int N, int K,
+                         float fp8_max, void* stream);
 
 /* Seeded synthetic inputs (role of genMat, utils.h:25-33, but counter-based so that any
  * slice can be generated independently).  Elements: N(0,1) rounded to nearest-even e4m3fn,

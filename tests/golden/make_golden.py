@@ -12,6 +12,8 @@ output of reference CODE run on seeded inputs:
                       genMat exactly as check.cu:155-167 builds them), fp8 bytes made by
                       torch's float8_e4m3fn cast, expected C from the reference's gemmCPU
                       (utils.h:65-76) on the dequantised operands -> bf16
+  quantizer_case.npz  fp32 matrices X, W and what the reference's quantize.py makes of them (e4m3fn bytes and inverse
+                      scales, re-laid out as the GEMM reads them): the expected output of the device-side quantisers
   quantize_case.npz   inputs produced by the reference's quantize.py (row-wise 1x128 scales
                       for A, quantize.py:43-67; 128x128 block scales for B, quantize.py:16-41,
                       dtype e4m3fn) from a seeded fp32 matrix pair, expected C from a
@@ -98,6 +100,22 @@ def quantize_case():
              b_scale=b_scale, C_f64=Cd, C_bf16=f32_to_bf16_bits(Cd.astype(np.float32)))
 
 
+def quantizer_case():
+    """Inputs AND outputs of the reference's quantisers (fp32 input, e4m3fn output), for the device-side quantiser."""
+    spec = importlib.util.spec_from_file_location("ref_quantize", os.path.join(REF, "quantize.py"))
+    q = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(q)
+    gen = torch.Generator().manual_seed(11)
+    X = torch.randn(144, 256, generator=gen) * torch.rand(144, 1, generator=gen) * 8.0
+    W = torch.randn(256, 256, generator=gen) * 0.3
+    X[3, 128:] = 0.0                                         # an all-zero group: exercises the 1e-12 clamp
+    A8, a_inv = q.to_float8_rowwise_scale(X, dtype=torch.float8_e4m3fn)
+    B8, b_inv = q.to_float8_block_scale(W, dtype=torch.float8_e4m3fn)
+    np.savez(os.path.join(HERE, "quantizer_case.npz"), X=X.numpy(), W=W.numpy(),
+             A=A8.view(torch.uint8).numpy().T.copy().ravel(), a_scale=a_inv.numpy().T.copy().ravel().astype(np.float32),
+             B=B8.view(torch.uint8).numpy().T.copy().ravel(), b_scale=b_inv.numpy().T.copy().ravel().astype(np.float32))
+
+
 if __name__ == "__main__":
     ref = helpers.ref_lib()
     if ref is None:
@@ -106,5 +124,6 @@ if __name__ == "__main__":
     genmat(ref)
     check_case(ref)
     quantize_case()
+    quantizer_case()
     for f in sorted(os.listdir(HERE)):
         print(f, os.path.getsize(os.path.join(HERE, f)))

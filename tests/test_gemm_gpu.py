@@ -50,12 +50,14 @@ FORCED = [
     dict(path=f.PATH_MN_SMALL, splits=2, tile_n=256),
     dict(path=f.PATH_MN_LARGE, splits=1, tile_n=256 | f.TILE_PAIR),      # 256 x 256 tile on a pair of CTAs
     dict(path=f.PATH_MN_SMALL, splits=2, tile_n=256 | f.TILE_PAIR),
+    dict(path=f.PATH_MN_SMALL, splits=2, tile_n=128 | f.SPLIT_WORKSPACE),  # split-K reduced through the workspace
+    dict(path=f.PATH_MN_SMALL, splits=2, tile_n=256 | f.SPLIT_WORKSPACE),
 ]
 
 
 def ids(cfgs):
-    return ["p%d-s%d-t%d%s" % (c["path"], c["splits"], c["tile_n"] & 0xFFF, "pair" if c["tile_n"] & f.TILE_PAIR else "")
-            for c in cfgs]
+    return ["p%d-s%d-t%d%s%s" % (c["path"], c["splits"], c["tile_n"] & 0xFFF, "pair" if c["tile_n"] & f.TILE_PAIR else "",
+                                 "ws" if c["tile_n"] & f.SPLIT_WORKSPACE else "") for c in cfgs]
 
 
 # ------------------------------------------------------------------ known answers ----------
@@ -170,15 +172,18 @@ def test_both_kernels_forced_on_named_configs(shape):
 
 # ------------------------------------------------------------------ properties -------------
 @pytest.mark.parametrize("shape,splits,tile_n", [((1024, 576, 7168), 7, 128), ((6144, 512, 7168), 6, 128),
-                                                 ((6144, 512, 7168), 3, 256 | 0x1000), ((6144, 512, 7168), 7, 256)],
-                         ids=["1024x576-s7-t128", "6144x512-s6-t128", "6144x512-s3-pair", "6144x512-s7-t256"])
+                                                 ((6144, 512, 7168), 3, 256 | 0x1000), ((6144, 512, 7168), 7, 256),
+                                                 ((1024, 576, 7168), 7, 128 | 0x2000), ((6144, 512, 7168), 6, 128 | 0x2000),
+                                                 ((6144, 512, 7168), 9, 128), ((6144, 512, 7168), 7, 256 | 0x2000)],
+                         ids=["1024x576-s7-t128", "6144x512-s6-t128", "6144x512-s3-pair", "6144x512-s7-t256",
+                              "1024x576-s7-t128-ws", "6144x512-s6-t128-ws", "6144x512-s9-t128-ws", "6144x512-s7-t256-ws"])
 def test_split_k_is_bit_deterministic(shape, splits, tile_n):
     # several work units per CTA; the workspace is poisoned with NaN before every run so that a partial sum
     # read before it was written, or left over from another run, cannot go unnoticed
     M, N, K = shape
     A, B, a_s, b_s = h.make_inputs(M, N, K, seed=3)
     dA, dB, dAs, dBs = to_dev(A, B, a_s, b_s)
-    ws = torch.zeros(f.workspace_bytes(M, N, K, f.PATH_MN_SMALL, splits, tile_n), dtype=torch.uint8, device=dev())
+    ws = torch.zeros(max(65536, f.workspace_bytes(M, N, K, f.PATH_MN_SMALL, splits, tile_n)), dtype=torch.uint8, device=dev())
     first = None
     for i in range(20):
         ws[65536:].fill_(0xFF)
@@ -246,19 +251,21 @@ def test_workspace_rules():
     lib = f.lib()
     args = (dA.data_ptr(), dB.data_ptr(), dAs.data_ptr(), dBs.data_ptr(), C.data_ptr(), M, N, K)
     small = torch.zeros(1024, dtype=torch.uint8, device=dev())
-    # forced split-K with too little workspace is an error, never a silent other path
-    assert lib.fp8bs_gemm_mn_small(*args, 4, small.data_ptr(), small.numel(), None) == -4
+    # forced split-K through the workspace with too little of it is an error, never a silent other path
+    assert lib.fp8bs_gemm_ex(*args, 0, N, f.PATH_MN_SMALL, 4, 128 | f.SPLIT_WORKSPACE, small.data_ptr(), small.numel(), None) == -4
+    # the cluster reduction needs none
+    assert lib.fp8bs_gemm_mn_small(*args, 4, None, 0, None) == 0
     # auto dispatch without workspace falls back to a full-K configuration and is still right
     assert lib.fp8bs_gemm(*args, None, 0, None) == 0
     torch.cuda.synchronize()
     assert_parity(h.oracle_gemm(A, B, a_s, b_s, M, N, K), C.view(torch.int16).cpu().numpy().view(np.uint16))
     # an explicit caller-owned workspace
-    need = f.workspace_bytes(M, N, K, f.PATH_MN_SMALL, 4, 128)
+    need = f.workspace_bytes(M, N, K, f.PATH_MN_SMALL, 4, 128 | f.SPLIT_WORKSPACE)
     ws = torch.empty(need, dtype=torch.uint8, device=dev())
     assert lib.fp8bs_workspace_init(ws.data_ptr(), need, None) == 0
     for _ in range(3):     # the counters re-arm themselves between calls
         C.fill_(float("nan"))
-        assert lib.fp8bs_gemm_mn_small(*args, 4, ws.data_ptr(), need, None) == 0
+        assert lib.fp8bs_gemm_ex(*args, 0, N, f.PATH_MN_SMALL, 4, 128 | f.SPLIT_WORKSPACE, ws.data_ptr(), need, None) == 0
         torch.cuda.synchronize()
         assert_parity(h.oracle_gemm(A, B, a_s, b_s, M, N, K), C.view(torch.int16).cpu().numpy().view(np.uint16))
     assert lib.fp8bs_last_device_status(None, None) == 0

@@ -42,11 +42,12 @@ def test_dispatch_policy_on_the_18_shapes():
     # large M*N -> the persistent full-K kernel; small M*N with K = 7168 -> split-K (README.md:99, 161)
     for (M, N, K) in f.SHAPES_18:
         path, splits, tile_n = f.select_path(M, N, K)
-        assert path in (f.PATH_MN_LARGE, f.PATH_MN_SMALL) and tile_n in (128, 256, 256 | f.TILE_PAIR)
+        assert path in (f.PATH_MN_LARGE, f.PATH_MN_SMALL)
+        assert (tile_n & ~f.SPLIT_WORKSPACE) in (128, 256, 256 | f.TILE_PAIR)
         assert 1 <= splits <= K // 128
         assert (path == f.PATH_MN_SMALL) == (splits > 1)
         ws = f.workspace_bytes(M, N, K)
-        assert (ws > 0) == (splits > 1)
+        assert (ws > 0) == bool(tile_n & f.SPLIT_WORKSPACE)        # cluster reductions need no workspace
     assert f.select_path(6144, 4608, 7168)[0] == f.PATH_MN_LARGE
     assert f.select_path(1024, 512, 7168)[0] == f.PATH_MN_SMALL
     assert f.select_path(1024, 576, 7168)[0] == f.PATH_MN_SMALL
@@ -61,7 +62,9 @@ def test_dispatch_is_deterministic_and_validates():
     with pytest.raises(f.Fp8bsError) as e:
         f.select_path(1000, 1536, 128)          # M % 16 != 0
     assert e.value.code == -3
-    assert f.workspace_bytes(1024, 512, 7168, f.PATH_MN_SMALL, 4, 128) == 65536 + 8 * 4 * 4 * 128 * 128 * 4
+    assert f.workspace_bytes(1024, 512, 7168, f.PATH_MN_SMALL, 4, 128 | f.SPLIT_WORKSPACE) == 65536 + 8 * 4 * 4 * 128 * 128 * 4
+    assert f.workspace_bytes(1024, 512, 7168, f.PATH_MN_SMALL, 4, 128) == 0          # reduced inside a cluster
+    assert f.workspace_bytes(1024, 512, 7168, f.PATH_MN_SMALL, 9, 128) > 0           # more than 8 splits: workspace
     assert f.workspace_bytes(1024, 512, 7168, f.PATH_MN_LARGE, 1, 0) == 0
     assert f.workspace_bytes(1024, 512, 7168, f.PATH_MN_LARGE, 2, 0) == 0     # invalid combination -> 0
 
@@ -87,7 +90,7 @@ def test_argument_errors_come_back_as_codes_without_touching_a_device():
     assert ex(fake, fake, fake, fake, fake, 128, 128, 256, 32, 256, 0, 0, 0, None, 0, None) == -5   # n0 % 64
     assert ex(fake, fake, fake, fake, fake, 128, 128, 256, 192, 256, 0, 0, 0, None, 0, None) == -5  # shard beyond n_total
     # forced split-K without a workspace
-    assert lib.fp8bs_gemm_mn_small(fake, fake, fake, fake, fake, 128, 128, 256, 2, None, 0, None) == -4
+    assert ex(fake, fake, fake, fake, fake, 128, 128, 256, 0, 128, 2, 2, 128 | f.SPLIT_WORKSPACE, None, 0, None) == -4
     assert lib.fp8bs_workspace_init(None, 1 << 20, None) == -1
     assert lib.fp8bs_workspace_init(fake, 16, None) == -4
 

@@ -29,8 +29,8 @@ def _inputs(M, N, K, seed):
 def test_static_scratch_matches_the_workspace_entry_point(M, N, K, splits):
     dev = torch.device("cuda:0")
     lib = f.lib()
-    need = f.workspace_bytes(M, N, K, f.PATH_MN_SMALL, splits, 0)
-    assert need <= f.STATIC_SCRATCH_BYTES
+    need = f.workspace_bytes(M, N, K, f.PATH_MN_SMALL, splits, f.SPLIT_WORKSPACE)     # what the static entry point uses
+    assert 0 < need <= f.STATIC_SCRATCH_BYTES
     ws = torch.zeros(max(need, 65536), dtype=torch.uint8, device=dev)
     for call in range(2):                                   # two calls in a row, different data each time
         (dA, dB, dAs, dBs), host = _inputs(M, N, K, seed=40 + call)
@@ -57,7 +57,7 @@ def test_static_scratch_matches_the_workspace_entry_point(M, N, K, splits):
 def test_static_scratch_refuses_what_does_not_fit():
     dev = torch.device("cuda:0")
     M, N, K = 6144, 4608, 256
-    assert f.workspace_bytes(M, N, K, f.PATH_MN_SMALL, 2, 0) > f.STATIC_SCRATCH_BYTES
+    assert f.workspace_bytes(M, N, K, f.PATH_MN_SMALL, 2, f.SPLIT_WORKSPACE) > f.STATIC_SCRATCH_BYTES
     dummy = torch.zeros(M * K + N * K, dtype=torch.uint8, device=dev)
     scales = torch.ones(M * 2 + 36 * 2, dtype=torch.float32, device=dev)
     C = torch.zeros((M, N), dtype=torch.bfloat16, device=dev)
