@@ -30,6 +30,7 @@ from .api import (  # noqa: F401
     float_to_e4m3fn,
     e4m3fn_to_float,
     fnuz_to_fn,
+    fnuz_to_fn_device,
     status_string,
     launch_count,
     last_device_status,

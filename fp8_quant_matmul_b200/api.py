@@ -42,6 +42,7 @@ _SIGS = {
     "fp8bs_workspace_bytes_ex": (_c.c_size_t, [_c.c_int] * 6),
     "fp8bs_workspace_init": (_c.c_int, [_c.c_void_p, _c.c_size_t, _c.c_void_p]),
     "fp8bs_last_device_status": (_c.c_int, [_c.c_void_p, _c.POINTER(_c.c_uint)]),
+    "fp8bs_selftest_wait_timeout": (_c.c_int, [_c.c_void_p]),
     "fp8bs_status_string": (_c.c_char_p, [_c.c_int]),
     "fp8bs_last_cuda_error": (_c.c_int, []),
     "fp8bs_launch_count": (_c.c_ulonglong, []),
@@ -56,6 +57,7 @@ _SIGS = {
     "fp8bs_gen_uniform_f32": (_c.c_int, [_c.c_void_p, _c.c_size_t, _c.c_uint64, _c.c_float, _c.c_float]),
     "fp8bs_float_to_e4m3fn": (_c.c_uint8, [_c.c_float]),
     "fp8bs_e4m3fn_to_float": (_c.c_float, [_c.c_uint8]),
+    "fp8bs_fnuz_to_fn_device": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_size_t, _c.c_void_p, _c.c_void_p]),
     "fp8bs_fnuz_to_fn": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_size_t, _c.POINTER(_c.c_size_t)]),
 }
 
@@ -151,6 +153,18 @@ def fnuz_to_fn(src):
         err.bad_index = bad.value
         raise err
     return dst
+
+
+def fnuz_to_fn_device(src, dst=None):
+    """Re-encode a CUDA uint8 tensor of e4m3fnuz bytes as e4m3fn bytes; returns (dst, number of inexact bytes)."""
+    torch = _torch()
+    if dst is None:
+        dst = torch.empty_like(src)
+    count = torch.zeros(1, dtype=torch.int32, device=src.device)
+    stream = torch.cuda.current_stream(src.device).cuda_stream
+    _check(lib().fp8bs_fnuz_to_fn_device(dst.data_ptr(), src.data_ptr(), src.numel(), count.data_ptr(), stream),
+           "fp8bs_fnuz_to_fn_device")
+    return dst, int(count.item())
 
 
 # ---------------------------------------------------------------- the operator ---------

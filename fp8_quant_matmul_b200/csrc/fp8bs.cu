@@ -647,6 +647,18 @@ int fp8bs_last_device_status(void* stream, unsigned int* detail)
     return FP8BS_OK;
 }
 
+int fp8bs_selftest_wait_timeout(void* stream)
+{
+    DeviceInfo* dev = nullptr;
+    const int rc = device_setup(&dev);
+    if (rc) return rc;
+    // about 20 ms at 2 GHz: long enough to be a real wait, short enough for a test
+    wait_timeout_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(dev->status_ptr, 40000000LL);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    CUDA_TRY(cudaGetLastError());
+    return FP8BS_OK;
+}
+
 const char* fp8bs_status_string(int status)
 {
     switch (status) {
@@ -816,6 +828,67 @@ int fp8bs_gemm_host(fp8bs_host_ctx* ctx, uint16_t* C, const void* A, const void*
     if (rc) return rc;
     CUDA_TRY(cudaMemcpyAsync(C, c->dC, static_cast<size_t>(M) * N * 2, cudaMemcpyDeviceToHost, c->stream));
     CUDA_TRY(cudaStreamSynchronize(c->stream));
+    return FP8BS_OK;
+}
+
+// ---- e4m3fnuz -> e4m3fn on the device -----------------------------------------------------------
+// One byte in, one byte out, 16 bytes per thread.  Same mapping as fp8bs_fnuz_to_fn; the eight magnitudes e4m3fn
+// cannot hold (odd multiples of 2^-10 below 2^-6) are rounded to the nearest even multiple of 2^-9 and counted.
+__device__ __forceinline__ uint32_t fnuz_to_fn_byte(uint32_t b, unsigned int& inexact)
+{
+    const uint32_t e = (b >> 3) & 0xFu, m = b & 7u, sign = b & 0x80u;
+    if (b == 0x80u) return 0x7Fu;                       // NaN stays NaN
+    if ((b & 0x7Fu) == 0u) return 0u;
+    if (e >= 2u) return b - 8u;                         // same mantissa, exponent field one lower
+    const uint32_t q = (e == 0u) ? m : 8u + m;          // value = q * 2^-10
+    uint32_t h = q >> 1;                                // -> h * 2^-9
+    if (q & 1u) { ++inexact; h += (h & 1u); }           // tie: round half to even
+    return sign | h;                                    // h <= 8; 8 is the encoding of 2^-6
+}
+
+__global__ void fnuz_to_fn_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, size_t n16,
+                                  const uint8_t* __restrict__ src_tail, uint8_t* __restrict__ dst_tail, int tail,
+                                  unsigned int* __restrict__ inexact_count)
+{
+    unsigned int inexact = 0;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n16;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        uint4 v = src[i];
+        uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            uint32_t o = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) o |= fnuz_to_fn_byte((w[k] >> (8 * j)) & 0xFFu, inexact) << (8 * j);
+            w[k] = o;
+        }
+        dst[i] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    if (blockIdx.x == 0 && static_cast<int>(threadIdx.x) < tail)
+        dst_tail[threadIdx.x] = static_cast<uint8_t>(fnuz_to_fn_byte(src_tail[threadIdx.x], inexact));
+    if (inexact && inexact_count) atomicAdd(inexact_count, inexact);
+}
+
+int fp8bs_fnuz_to_fn_device(void* dst, const void* src, size_t n, unsigned int* inexact_count, void* stream)
+{
+    if (!dst || !src) return FP8BS_ERR_NULL;
+    if ((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src)) & 15u) return FP8BS_ERR_ALIGN;
+    DeviceInfo* dev = nullptr;
+    const int rc = device_setup(&dev);
+    if (rc) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (inexact_count) CUDA_TRY(cudaMemsetAsync(inexact_count, 0, sizeof(unsigned int), st));
+    const size_t n16 = n / 16;
+    const int tail = static_cast<int>(n % 16);
+    size_t blocks = (n16 + 255) / 256;
+    const size_t cap = static_cast<size_t>(dev->sm_count) * 8;
+    if (blocks > cap) blocks = cap;
+    if (blocks == 0) blocks = 1;
+    fnuz_to_fn_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(
+        static_cast<const uint4*>(src), static_cast<uint4*>(dst), n16, static_cast<const uint8_t*>(src) + n16 * 16,
+        static_cast<uint8_t*>(dst) + n16 * 16, tail, inexact_count);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    CUDA_TRY(cudaGetLastError());
     return FP8BS_OK;
 }
 

@@ -96,7 +96,11 @@ struct TileCfg {
     static constexpr int PROMO_WARPS = 8;             // 4 TMEM lane quarters x 2 column groups
     static constexpr int PROMO_THREADS = 32 * PROMO_WARPS;
     static constexpr int THREADS = 128 + PROMO_THREADS;
-    static constexpr int STG_BYTES = PROMO_WARPS * 4096;   // per warp: one store box, 32 rows x 64 bf16 columns
+    // per warp: store boxes of 32 rows x 64 bf16 columns.  Single-CTA 256-wide tiles get two (one per 64-column half of
+    // a thread's 128 columns), so the second half need not wait for the first store to drain; pair tiles, used for long
+    // K where the epilogue is a small part, keep one box and the extra pipeline stage instead.
+    static constexpr int NSTG = (CG == 1) ? COLS / 64 : 1;
+    static constexpr int STG_BYTES = PROMO_WARPS * 4096 * NSTG;
     static constexpr int SRING = 8;                   // a_scale ring entries (128 floats each)
     static constexpr int SRING_BYTES = SRING * 512;
     static constexpr int SMEM_LIMIT = 232448;         // 227 KB per CTA
@@ -127,7 +131,8 @@ __device__ __forceinline__ long long prof_now_ns() { unsigned long long t; asm v
 
 // Spin on an mbarrier phase with a time limit.  Returns false if the CTA is aborting.
 __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                             unsigned int* status, uint32_t code)
+                                             unsigned int* status, uint32_t code,
+                                             long long limit_cycles = WAIT_LIMIT_CYCLES)
 {
     if (ptx::mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
@@ -136,7 +141,7 @@ __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, vola
         for (int i = 0; i < 64; ++i)
             if (ptx::mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
-        if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+        if (clock64() - t0 > limit_cycles) {
             *abort_flag = 1u;
             atomicMax(status, code | (static_cast<uint32_t>(blockIdx.x) << 8));
             return false;
@@ -177,11 +182,13 @@ struct FloatCols {
 // Converts 64 columns of this thread's row to bf16 (round to nearest even) into a 32-row x 128-byte staging
 // box laid out as the 128-byte-swizzled TMA store expects; then the warp's lane 0 issues the store.
 // The box covers rows [row0, row0 + 32) and columns [col, col + 64); lane = row within the box.
-template <class Cols>
+// PENDING: how many of this thread's most recent stores may still be reading shared memory (1 when the warp
+// alternates between two boxes: only the store before the last one used this box).
+template <int PENDING, class Cols>
 __device__ __forceinline__ void stage_and_store_64(const CUtensorMap* tmC, uint8_t* stg, uint32_t stg_addr, int lane,
                                                    const Cols cols, int col, int row0, int M, int N)
 {
-    if (lane == 0) ptx::tma_store_wait_read<0>();      // the previous store out of this box has read it
+    if (lane == 0) ptx::tma_store_wait_read<PENDING>();      // the previous store out of this box has read it
     __syncwarp();
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
@@ -199,6 +206,23 @@ __device__ __forceinline__ void stage_and_store_64(const CUtensorMap* tmC, uint8
         ptx::tma_store_2d(tmC, stg_addr, col, row0);   // rows >= M and columns >= N are clipped by the hardware
         ptx::tma_store_commit();
     }
+}
+
+// Self-test of the failure path: one warp waits, with a short limit, on a barrier that nothing ever arrives on.
+// The wait must give up, record DS_TIMEOUT_SELFTEST in the status word and the kernel must end normally.
+constexpr uint32_t DS_TIMEOUT_SELFTEST = 9;
+__global__ void wait_timeout_selftest_kernel(unsigned int* status, long long limit_cycles)
+{
+    __shared__ uint64_t bar;
+    __shared__ uint32_t abort_word;
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(ptx::smem_u32(&bar), 1);
+        abort_word = 0u;
+        ptx::fence_mbar_init();
+    }
+    __syncthreads();
+    const bool ok = wait_bounded(ptx::smem_u32(&bar), 0u, &abort_word, status, DS_TIMEOUT_SELFTEST, limit_cycles);
+    (void)ok;
 }
 
 template <int BN, int CG, int MODE>
@@ -425,8 +449,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         const int quarter = warp & 3;            // TMEM lanes this warp may read: 32*quarter ..
         const int grp = pw >> 2;                 // which half of the tile's columns
         const int row_in_tile = quarter * 32 + lane;
-        uint8_t* my_stg = stg_ptr + pw * 4096;
-        const uint32_t my_stg_addr = stg_base + pw * 4096;
+        uint8_t* my_stg = stg_ptr + pw * 4096 * Cfg::NSTG;
+        const uint32_t my_stg_addr = stg_base + pw * 4096 * Cfg::NSTG;
         uint32_t lead_tempty = tempty_bar(0);
         if constexpr (CG == 2) lead_tempty = ptx::mapa(tempty_bar(0), 0);
         uint32_t ait = 0;
@@ -523,9 +547,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 if (!ok) break;
                 // ---- epilogue: fp32 -> bf16 (round to nearest even), staged, TMA store ----
 #pragma unroll
-                for (int h = 0; h < Cfg::COLS / 64; ++h)
-                    stage_and_store_64(&tmC, my_stg, my_stg_addr, lane, PackedCols{acc[2 * h], acc[2 * h + 1]},
-                                       ncol0 + h * 64, m0 + quarter * 32, p.M, p.N);
+                for (int h = 0; h < Cfg::COLS / 64; ++h) {
+                    const int box = (Cfg::NSTG == 2) ? h : 0;
+                    stage_and_store_64<Cfg::NSTG - 1>(&tmC, my_stg + box * 4096, my_stg_addr + box * 4096, lane,
+                                                      PackedCols{acc[2 * h], acc[2 * h + 1]}, ncol0 + h * 64,
+                                                      m0 + quarter * 32, p.M, p.N);
+                }
             } else if constexpr (MODE == 2) {
                 // ---- split-K through the cluster: leave this K range's partial tile in shared memory ----
                 // The stage buffers are free: every MMA of this CTA has completed (the last TMEM buffer was full)
@@ -597,7 +624,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                                 sum[4 * j + 3] += v.w;
                             }
                         }
-                        stage_and_store_64(&tmC, my_stg, my_stg_addr, lane, FloatCols{sum}, ncol0 + h * 64, m0 + quarter * 32, p.M, p.N);
+                        stage_and_store_64<0>(&tmC, my_stg, my_stg_addr, lane, FloatCols{sum}, ncol0 + h * 64, m0 + quarter * 32, p.M, p.N);
                     }
                 }
             }

@@ -132,6 +132,11 @@ int fp8bs_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
  * record).  *detail (optional) receives the raw device status word. */
 int fp8bs_last_device_status(void* stream, unsigned int* detail);
 
+/* Failure-path self-test (no counterpart in the reference, which has no error handling): launches one warp that
+ * waits, with a limit of about 20 ms, on a barrier nothing arrives on.  The wait gives up, the kernel ends normally,
+ * and the next fp8bs_last_device_status returns FP8BS_ERR_DEVICE_TIMEOUT (detail & 0xFF == 9); the context stays usable. */
+int fp8bs_selftest_wait_timeout(void* stream);
+
 const char* fp8bs_status_string(int status);
 /* cudaError_t of the most recent failing CUDA call made by this thread (0 if none). */
 int fp8bs_last_cuda_error(void);
@@ -187,6 +192,12 @@ float fp8bs_e4m3fn_to_float(uint8_t b);
  * of equal value.  Returns FP8BS_ERR_FP8_BYTE at the first byte whose value e4m3fn cannot
  * hold (NaN 0x80, or an odd multiple of 2^-10 below 2^-6); *bad_index receives its index. */
 int fp8bs_fnuz_to_fn(uint8_t* dst, const uint8_t* src, size_t n, size_t* bad_index);
+
+/* The same re-encoding on the device, for operands that already live in GPU memory in the reference's format
+ * (dst may equal src; both 16-byte aligned).  Bytes without an equal e4m3fn value do not stop it: NaN (0x80) becomes
+ * the e4m3fn NaN, and the odd multiples of 2^-10 below 2^-6 are rounded to the nearest even multiple of 2^-9; their
+ * number is stored in *inexact_count (a device pointer, may be NULL).  Asynchronous on `stream`. */
+int fp8bs_fnuz_to_fn_device(void* dst, const void* src, size_t n, unsigned int* inexact_count, void* stream);
 
 #ifdef __cplusplus
 }

@@ -319,3 +319,18 @@ def test_host_context_end_to_end():
             assert_parity(h.oracle_gemm(A, B, a_s, b_s, M, N, K), hC.reshape(M, N))
     finally:
         ctx.close()
+
+
+def test_bounded_wait_reports_a_timeout_and_leaves_the_context_usable():
+    # failure detection without a GPU fault: a wait on a barrier nothing sets runs out, the kernel returns a status
+    lib = f.lib()
+    f.last_device_status()                                   # start from a clean record
+    assert lib.fp8bs_selftest_wait_timeout(None) == 0
+    with pytest.raises(f.Fp8bsError) as e:
+        f.last_device_status()
+    assert e.value.code == -8 and (e.value.detail & 0xFF) == 9
+    f.last_device_status()                                   # the record was cleared
+    # and the GPU still computes
+    M, N, K = 128, 128, 256
+    A, B, a_s, b_s = h.make_inputs(M, N, K, seed=2)
+    assert_parity(h.oracle_gemm(A, B, a_s, b_s, M, N, K), run_gemm(A, B, a_s, b_s, M, N, K))

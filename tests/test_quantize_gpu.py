@@ -78,3 +78,38 @@ def test_quantiser_argument_errors():
     assert lib.fp8bs_quantize_rowwise(*args, 128, 200, 448.0, None) == -2          # K % 128
     assert lib.fp8bs_quantize_rowwise(*args, 120, 256, 448.0, None) == -3          # rows % 16
     assert lib.fp8bs_quantize_block(*args, 128, 256, 500.0, None) == -5            # beyond the e4m3fn range
+
+
+def test_fnuz_bytes_from_the_reference_format_are_ingested_on_the_device():
+    # operands stored as e4m3fnuz (the reference's element type, check.cu:17-21): convert on the device, run the GEMM,
+    # compare with the CPU checker decoding the ORIGINAL bytes as fnuz
+    dev = torch.device("cuda:0")
+    M, N, K = 256, 256, 512
+    A_fn, B_fn, a_s, b_s = h.make_inputs(M, N, K, seed=77)              # values common to both dialects
+    to_fnuz = lambda b: np.where((b & 0x7F) == 0, 0, b + 8).astype(np.uint8)
+    A_z, B_z = to_fnuz(A_fn), to_fnuz(B_fn)
+    dA, nA = f.fnuz_to_fn_device(torch.from_numpy(A_z).to(dev))
+    dB, nB = f.fnuz_to_fn_device(torch.from_numpy(B_z).to(dev))
+    assert nA == 0 and nB == 0
+    assert np.array_equal(dA.cpu().numpy(), A_fn) and np.array_equal(dB.cpu().numpy(), B_fn)
+    C = f.gemm(dA, dB, torch.from_numpy(a_s).to(dev), torch.from_numpy(b_s).to(dev), None, M, N, K)
+    ref = h.oracle_gemm(A_z, B_z, a_s, b_s, M, N, K, dialect=1)
+    bad, first, maxerr = h.mismatches(ref, C.view(torch.int16).cpu().numpy().view(np.uint16))
+    assert bad == 0, (bad, first, maxerr)
+    # every byte value: agrees with the host converter where that one accepts the byte; the rest is counted
+    allb = np.arange(256, dtype=np.uint8).repeat(3)[:-5]               # 763 bytes: exercises the ragged tail too
+    d, inexact = f.fnuz_to_fn_device(torch.from_numpy(allb).to(dev))
+    got = d.cpu().numpy()
+    L = h.oracle_lib()
+    n_bad = 0
+    for s_, g_ in zip(allb, got):
+        want = L.oracle_e4m3fnuz_to_float(int(s_))
+        have = L.oracle_e4m3fn_to_float(int(g_))
+        if want != want:
+            assert have != have                                          # NaN -> NaN
+        elif want == have:
+            continue
+        else:
+            n_bad += 1
+            assert abs(have - want) <= 2.0 ** -10                        # rounded to the neighbouring multiple of 2^-9
+    assert n_bad == inexact and inexact > 0
