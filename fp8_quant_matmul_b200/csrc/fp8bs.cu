@@ -260,12 +260,12 @@ static int encode_operand_map(CUtensorMap* tm, const void* base, int mn, int K)
     return FP8BS_OK;
 }
 
-// a_scale as a 2-D fp32 tensor {M, K/128}; one box = the 128 scales of a tile's rows for one K block.
+// a_scale as a 2-D fp32 tensor {M, K/128}; one box = the scales of a tile's 128 rows for SCALE_GROUP K blocks.
 static int encode_scale_map(CUtensorMap* tm, const float* base, int M, int KB)
 {
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(M), static_cast<cuuint64_t>(KB)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(M) * 4};
-    const cuuint32_t box[2] = {128u, 1u};
+    const cuuint32_t box[2] = {128u, static_cast<cuuint32_t>(SCALE_GROUP)};
     const cuuint32_t estr[2] = {1u, 1u};
     const CUresult r = g_encode_tiled(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides,
                                       box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,

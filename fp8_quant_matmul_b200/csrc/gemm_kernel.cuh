@@ -21,7 +21,9 @@
 //                 fp32 workspace and whoever finishes a tile last adds them.
 //
 // Warp roles (no __syncthreads in the main loop; registers are moved from the first warpgroup
-// to the promotion warps with setmaxnreg):
+// to the promotion warps with setmaxnreg: 168 at launch, then 64 for warps 0-3 and 216 for the
+// rest, which the compiler fits without a single spill; 56/224 left a few spilled words in the
+// promotion loop and cost 8-15 % on the long-K shapes):
 //   warp 0     TMA producer for A and B.  Both operands are MN-major in global memory, so a box
 //              of {128 m or n, 128 k} lands in shared memory as 128 rows (k) of 128 bytes,
 //              128-byte swizzled: the MN-major operand layout tcgen05.mma reads directly.  The
@@ -30,13 +32,14 @@
 //   warp 1     MMA issuer.  Per 128-K block: four tcgen05.mma kind::f8f6f4 (K = 32 each) into a
 //              fresh TMEM buffer (the first one overwrites), then commits that free the
 //              shared-memory stage and publish the TMEM buffer.
-//   warp 2     TMA producer for a_scale: 128 floats per K block into a small ring, so the
+//   warp 2     TMA producer for a_scale: boxes of 128 rows x 8 K blocks into a small ring, so the
 //              promotion warps never wait on a global load (mn_large.hip:50-55 stages the
-//              pre-multiplied scales in LDS for the same reason).
+//              pre-multiplied scales in LDS for the same reason) and pay one barrier round trip
+//              per 8 K blocks.
 //   warp 3     idle (completes the warpgroup that gives up its registers).
 //   warps 4..  promotion + epilogue.  TMEM lane = C row, so a thread owns one row and 128
-//              columns; per K block it reads the partial sums with tcgen05.ld (next chunk in
-//              flight while the current one is accumulated) and does
+//              columns; per K block it reads the partial sums with tcgen05.ld, 64 columns at a
+//              time, and does
 //              acc = fma(a_scale*b_scale, partial, acc) two columns at a time (mn_large.hip:99-106).
 //              The running sums stay in registers, so the MMA warp is already filling TMEM for
 //              the next tile while these warps convert to bf16, stage through swizzled shared
@@ -78,6 +81,11 @@ struct GemmParams {
 #endif
 };
 
+// a_scale reaches shared memory in boxes of 128 rows x SCALE_GROUP K blocks (the tensor map's box, see the host side):
+// one barrier round trip per SCALE_GROUP K blocks instead of one per block.  Measured on B200 with the promotion loop
+// otherwise unchanged: a per-block hand-off cost ~160 cycles per K block of a loop that has ~512 to spend.
+constexpr int SCALE_GROUP = 8;
+
 template <int BN, int CG>
 struct TileCfg {
     static_assert(BN == 128 || BN == 256, "tile width");
@@ -101,8 +109,9 @@ struct TileCfg {
     // K where the epilogue is a small part, keep one box and the extra pipeline stage instead.
     static constexpr int NSTG = (CG == 1) ? COLS / 64 : 1;
     static constexpr int STG_BYTES = PROMO_WARPS * 4096 * NSTG;
-    static constexpr int SRING = 8;                   // a_scale ring entries (128 floats each)
-    static constexpr int SRING_BYTES = SRING * 512;
+    static constexpr int SGRP = SCALE_GROUP;          // K blocks per a_scale ring entry (one TMA box {128 rows, SGRP})
+    static constexpr int SRING = 4;                   // a_scale ring entries
+    static constexpr int SRING_BYTES = SRING * SGRP * 512;
     static constexpr int SMEM_LIMIT = 232448;         // 227 KB per CTA
     static constexpr int FIXED = 1024 + STG_BYTES + SRING_BYTES + 512;
     static constexpr int STAGES = (SMEM_LIMIT - FIXED) / STAGE_BYTES;
@@ -121,7 +130,13 @@ constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;  // about one second
 #define PROF_OUT(slot, name) p.prof[blockIdx.x * 16 + (slot)] = (name)
 __device__ __forceinline__ long long prof_now_ns() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return static_cast<long long>(t); }
 #define PROF_STAMP(slot) p.prof[blockIdx.x * 16 + (slot)] = prof_now_ns()
+#define PROF_TRACE(ev, idx) do { if (blockIdx.x == 0 && (idx) < 128u) p.prof[4096 + (ev) * 128 + (idx)] = clock64(); } while (0)
+#define PROF_CLK0() const long long prof_c0__ = clock64()
+#define PROF_CLK1(slot) p.prof[blockIdx.x * 16 + (slot)] = clock64() - prof_c0__
 #else
+#define PROF_CLK0()
+#define PROF_CLK1(slot)
+#define PROF_TRACE(ev, idx)
 #define PROF_DECL(name)
 #define PROF_T0()
 #define PROF_ADD(name)
@@ -137,9 +152,8 @@ __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, vola
     if (ptx::mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (;;) {
-#pragma unroll 1
-        for (int i = 0; i < 64; ++i)
-            if (ptx::mbar_try_wait(bar, parity)) return true;
+        // parked in hardware for up to 8 us per try: no issue slots are spent while waiting
+        if (ptx::mbar_try_wait_parked(bar, parity, 8192u)) return true;
         if (*abort_flag) return false;
         if (clock64() - t0 > limit_cycles) {
             *abort_flag = 1u;
@@ -262,6 +276,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    PROF_CLK0();
     if (threadIdx.x == 0) { PROF_STAMP(8); }
     const uint32_t rank = (CG == 2) ? ptx::cluster_ctarank() : 0u;     // 0 = leader of the pair (MODE 2: not used)
     const int group_id = blockIdx.x / CG;                               // which tile walker this CTA belongs to
@@ -324,7 +339,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     };
 
     if (warp < 4) {
-        ptx::setmaxnreg_dec<56>();
+        ptx::setmaxnreg_dec<64>();
         if (warp == 0 && lane == 0) {
             // ---------------------------------------------------- TMA producer: A and B ----
             uint32_t it = 0;
@@ -344,6 +359,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     ok = wait_bounded(empty_bar(s), ph ^ 1u, abort_flag, p.status, DS_TIMEOUT_STAGE_EMPTY);
                     PROF_ADD(w_empty); }
                     if (!ok) break;
+                    PROF_TRACE(6, it);
                     const uint32_t a_dst = stage_base + s * Cfg::STAGE_BYTES;
                     if constexpr (CG == 2) {
                         // both CTAs' bytes are counted on the leader's barrier, which the MMA warp waits on
@@ -390,10 +406,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     ok = wait_bounded(tempty_bar(b), bph ^ 1u, abort_flag, p.status, DS_TIMEOUT_TMEM_EMPTY);
                     PROF_ADD(w_tempty); }
                     if (!ok) break;
+                    PROF_TRACE(0, it);
                     { PROF_T0();
                     ok = wait_bounded(full_bar(s), ph, abort_flag, p.status, DS_TIMEOUT_STAGE_FULL);
                     PROF_ADD(w_full); }
                     if (!ok) break;
+                    PROF_TRACE(1, it);
 #ifdef FP8BS_PROFILE
                     if (it == 0) { PROF_STAMP(10); }
 #endif
@@ -418,6 +436,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                         ptx::mma_commit(empty_bar(s));
                         ptx::mma_commit(tfull_bar(b));
                     }
+                    PROF_TRACE(2, it);
                 }
             }
 #ifdef FP8BS_PROFILE
@@ -431,20 +450,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             for (int u = group_id; u < units && ok; u += num_groups) {
                 int tile, m0, n0, kb0, kb1;
                 decode(u, tile, m0, n0, kb0, kb1);
-                for (int kb = kb0; kb < kb1; ++kb, ++sit) {
+                for (int kb = kb0; kb < kb1; kb += Cfg::SGRP, ++sit) {
                     const int i = sit % SRING;
                     const uint32_t ph = (sit / SRING) & 1u;
                     ok = wait_bounded(sempty_bar(i), ph ^ 1u, abort_flag, p.status, DS_TIMEOUT_SCALE_EMPTY);
                     if (!ok) break;
-                    ptx::mbar_arrive_expect_tx(sfull_bar(i), 512);
-                    ptx::tma_load_2d(sring_base + i * 512, &tmAs, m0, kb, sfull_bar(i));   // rows >= M read as 0
+                    // a whole box is always written and counted: rows >= M and K blocks past the end read as 0
+                    ptx::mbar_arrive_expect_tx(sfull_bar(i), Cfg::SGRP * 512);
+                    ptx::tma_load_2d(sring_base + i * (Cfg::SGRP * 512), &tmAs, m0, kb, sfull_bar(i));
                 }
             }
         }
         __syncwarp();
     } else {
         // -------------------------------------------------------- promotion + epilogue ------
-        ptx::setmaxnreg_inc<224>();
+        ptx::setmaxnreg_inc<216>();
         const int pw = warp - 4;
         const int quarter = warp & 3;            // TMEM lanes this warp may read: 32*quarter ..
         const int grp = pw >> 2;                 // which half of the tile's columns
@@ -454,6 +474,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         uint32_t lead_tempty = tempty_bar(0);
         if constexpr (CG == 2) lead_tempty = ptx::mapa(tempty_bar(0), 0);
         uint32_t ait = 0;
+        uint32_t sgit = 0;                       // a_scale ring entries consumed so far
         bool ok = true;
         PROF_DECL(w_sfull); PROF_DECL(w_tfull); PROF_DECL(t_fma); PROF_DECL(t_epi);
         for (int u = group_id; u < units; u += num_groups) {
@@ -494,14 +515,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 }
                 const float bl = __shfl_sync(0xffffffffu, bl_vec, kj) * p.elem_scale;
                 const float bh = __shfl_sync(0xffffffffu, bh_vec, kj) * p.elem_scale;
-                // a_scale of this row and block, from the ring
-                const int si = ait % SRING;
-                { PROF_T0();
-                ok = wait_bounded(sfull_bar(si), (ait / SRING) & 1u, abort_flag, p.status, DS_TIMEOUT_SCALE_FULL);
-                PROF_ADD(w_sfull); }
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                const float as = sring_ptr[si * 128 + row_in_tile];     // released at the end of the iteration
+                // a_scale of this row and block, from the ring: one entry holds SGRP consecutive K blocks
+                const int kr = (kb - kb0) % Cfg::SGRP;
+                const int si = sgit % SRING;
+                if (kr == 0) {
+                    PROF_T0();
+                    ok = wait_bounded(sfull_bar(si), (sgit / SRING) & 1u, abort_flag, p.status, DS_TIMEOUT_SCALE_FULL);
+                    PROF_ADD(w_sfull);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                }
+                if (pw == 0 && lane == 0) PROF_TRACE(3, ait);
+                const float as = sring_ptr[(si * Cfg::SGRP + kr) * 128 + row_in_tile];   // entry released below
                 const float s_lo = as * bl, s_hi = as * bh;
 
                 const int b = ait % NBUF;
@@ -510,6 +535,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 PROF_ADD(w_tfull); }
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
+                if (pw == 0 && lane == 0) PROF_TRACE(4, ait);
                 PROF_T0();
                 ptx::tc_fence_after_sync();
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
@@ -525,17 +551,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     ptx::fma32_from64_0(acc[2 * q], v, (2 * q >= hi_from) ? s_hi2 : s_lo2);
                     ptx::fma32_from64_32(acc[2 * q + 1], v, (2 * q + 1 >= hi_from) ? s_hi2 : s_lo2);
                 }
-                // Release the TMEM buffer and the a_scale ring entry only now, after the FMAs that consumed them.
-                // An arrive placed straight after the shared-memory read of a_scale (its value not yet used) let
-                // the producer refill the entry before a slow warp's read had completed: rare 32-row blocks scaled
-                // with the a_scale of the work unit eight K blocks later.
+                // Release the TMEM buffer, and after its last K block the a_scale ring entry, only now: after the
+                // FMAs that consumed them.  An arrive placed straight after the shared-memory read of a_scale (its
+                // value not yet used) let the producer refill the entry before a slow warp's read had completed:
+                // rare 32-row blocks scaled with the a_scale of a later work unit.
                 ptx::tc_fence_before_sync();
                 __syncwarp();
+                if (pw == 0 && lane == 0) PROF_TRACE(5, ait);
+                const bool entry_done = (kr == Cfg::SGRP - 1) || (kb == kb1 - 1);
                 if (lane == 0) {
                     if constexpr (CG == 2) ptx::mbar_arrive_cluster(lead_tempty + 8u * b);
                     else ptx::mbar_arrive(tempty_bar(b));
-                    ptx::mbar_arrive(sempty_bar(si));
+                    if (entry_done) ptx::mbar_arrive(sempty_bar(si));
                 }
+                if (entry_done) ++sgit;
                 PROF_ADD(t_fma);
             }
 #ifdef FP8BS_PROFILE
@@ -687,7 +716,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if constexpr (CG == 2) ptx::tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
         else ptx::tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
     }
-    if (threadIdx.x == 0) { PROF_STAMP(14); }
+    if (threadIdx.x == 0) { PROF_STAMP(14); PROF_CLK1(15); }
 }
 
 }  // namespace fp8bs
