@@ -402,16 +402,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     const uint32_t ph = (it / STAGES) & 1u;
                     const int b = ait % NBUF;
                     const uint32_t bph = (ait / NBUF) & 1u;
-                    { PROF_T0();
-                    ok = wait_bounded(tempty_bar(b), bph ^ 1u, abort_flag, p.status, DS_TIMEOUT_TMEM_EMPTY);
-                    PROF_ADD(w_tempty); }
-                    if (!ok) break;
-                    PROF_TRACE(0, it);
+                    // operands first (they are usually there already), then the TMEM buffer: nothing but the MMA
+                    // issue stands between the promotion warps' release of the buffer and its reuse
                     { PROF_T0();
                     ok = wait_bounded(full_bar(s), ph, abort_flag, p.status, DS_TIMEOUT_STAGE_FULL);
                     PROF_ADD(w_full); }
                     if (!ok) break;
                     PROF_TRACE(1, it);
+                    { PROF_T0();
+                    ok = wait_bounded(tempty_bar(b), bph ^ 1u, abort_flag, p.status, DS_TIMEOUT_TMEM_EMPTY);
+                    PROF_ADD(w_tempty); }
+                    if (!ok) break;
+                    PROF_TRACE(0, it);
 #ifdef FP8BS_PROFILE
                     if (it == 0) { PROF_STAMP(10); }
 #endif
@@ -427,14 +429,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                         if constexpr (CG == 2) ptx::mma_f8f6f4_pair(d, adesc + step, bdesc + step, idesc, j > 0 ? 1u : 0u);
                         else ptx::mma_f8f6f4(d, adesc + step, bdesc + step, idesc, j > 0 ? 1u : 0u);
                     }
+                    // the promotion warps wait on this one; the producer is several stages ahead
                     if constexpr (CG == 2) {
+                        ptx::mma_commit_pair(tfull_bar(b) + peer_base);
+                        ptx::mma_commit_pair(tfull_bar(b));
                         ptx::mma_commit_pair(empty_bar(s));
                         ptx::mma_commit_pair(empty_bar(s) + peer_base);
-                        ptx::mma_commit_pair(tfull_bar(b));
-                        ptx::mma_commit_pair(tfull_bar(b) + peer_base);
                     } else {
-                        ptx::mma_commit(empty_bar(s));
                         ptx::mma_commit(tfull_bar(b));
+                        ptx::mma_commit(empty_bar(s));
                     }
                     PROF_TRACE(2, it);
                 }
@@ -548,23 +551,30 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 #pragma unroll
                 for (int q = 0; q < Cfg::COLS / 64; ++q) {
                     ptx::tmem_ld_x64_sync(taddr + q * 64, v);
+                    if (q == Cfg::COLS / 64 - 1) {
+                        // The last columns of the buffer are in registers: hand the TMEM buffer back now, so that
+                        // the hand-off to the MMA warp overlaps the FMAs below instead of following them.
+                        ptx::tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) {
+                            if constexpr (CG == 2) ptx::mbar_arrive_cluster(lead_tempty + 8u * b);
+                            else ptx::mbar_arrive(tempty_bar(b));
+                        }
+                    }
                     ptx::fma32_from64_0(acc[2 * q], v, (2 * q >= hi_from) ? s_hi2 : s_lo2);
                     ptx::fma32_from64_32(acc[2 * q + 1], v, (2 * q + 1 >= hi_from) ? s_hi2 : s_lo2);
                 }
-                // Release the TMEM buffer, and after its last K block the a_scale ring entry, only now: after the
-                // FMAs that consumed them.  An arrive placed straight after the shared-memory read of a_scale (its
-                // value not yet used) let the producer refill the entry before a slow warp's read had completed:
-                // rare 32-row blocks scaled with the a_scale of a later work unit.
-                ptx::tc_fence_before_sync();
-                __syncwarp();
+                // Release the a_scale ring entry after its last K block, and only after the FMAs that consumed the
+                // value.  An arrive placed straight after the shared-memory read of a_scale (its value not yet
+                // used) let the producer refill the entry before a slow warp's read had completed: rare 32-row
+                // blocks scaled with the a_scale of a later work unit.
                 if (pw == 0 && lane == 0) PROF_TRACE(5, ait);
                 const bool entry_done = (kr == Cfg::SGRP - 1) || (kb == kb1 - 1);
-                if (lane == 0) {
-                    if constexpr (CG == 2) ptx::mbar_arrive_cluster(lead_tempty + 8u * b);
-                    else ptx::mbar_arrive(tempty_bar(b));
-                    if (entry_done) ptx::mbar_arrive(sempty_bar(si));
+                if (entry_done) {
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(sempty_bar(si));
+                    ++sgit;
                 }
-                if (entry_done) ++sgit;
                 PROF_ADD(t_fma);
             }
 #ifdef FP8BS_PROFILE
