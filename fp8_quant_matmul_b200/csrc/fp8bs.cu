@@ -152,8 +152,8 @@ constexpr int SM_TARGET = 148;   // B200; the dispatch is a pure function of the
 
 // Estimated run time of a configuration in microseconds.  The constants come from a measured sweep of
 // every configuration over the 18 benchmark shapes on a B200 (power-capped, cold L2):
-//   per 128-K block of one work unit: 0.44 us (128-wide tile), 0.60 us (256-wide), 0.565 us (256 x 256 pair);
-//   per work unit (tile switch, epilogue): 0.35 / 0.9 / 1.6 us;  per launch: 3.5 us;
+//   per 128-K block of one work unit: 0.44 us (128-wide tile), 0.53 us (256-wide), 0.60 us (256 x 256 pair);
+//   per work unit (tile switch, epilogue): 0.35 / 1.2 / 2.0 us;  per launch: 3.5 us;
 //   split-K through a workspace: 3.5 us + 1 us per split and 128 columns for the partial-sum round trip, doubled
 //   when a CTA has to walk more than one unit (the last-arriver reduction then delays the next unit);
 //   split-K inside a cluster: one CTA per (tile, K range); the number of clusters that fit on the GPU at once is
@@ -167,8 +167,8 @@ static double config_cost(int M, int N, int K, int tile_n, int splits, int cg, i
     const int tiles = ceil_div(M, 128 * cg) * ceil_div(N, tile_n);
     const int units = tiles * splits;
     const int waves = (mode == 2) ? ceil_div(tiles, kMaxActiveClusters[splits]) : ceil_div(units, SM_TARGET / cg);
-    const double per_kb = (cg == 2) ? 0.565 : (tile_n == 256 ? 0.60 : 0.44);
-    const double per_unit = (cg == 2) ? 1.6 : (tile_n == 256 ? 0.9 : 0.35);
+    const double per_kb = (cg == 2) ? 0.60 : (tile_n == 256 ? 0.53 : 0.44);
+    const double per_unit = (cg == 2) ? 2.0 : (tile_n == 256 ? 1.2 : 0.35);
     double cost = 3.5 + waves * (ceil_div(KB, splits) * per_kb + per_unit);
     if (splits > 1 && mode == 2) {
         cost += (tile_n == 256 ? 3.0 : 2.0) + 0.5 * splits * (tile_n / 128);

@@ -125,12 +125,21 @@ constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;  // about one second
 
 #ifdef FP8BS_PROFILE
 #define PROF_DECL(name) long long name = 0
+#if FP8BS_PROFILE >= 2   // per-wait timers: they perturb the loops they measure
 #define PROF_T0() const long long prof_t0__ = clock64()
 #define PROF_ADD(name) name += clock64() - prof_t0__
+#else
+#define PROF_T0()
+#define PROF_ADD(name)
+#endif
 #define PROF_OUT(slot, name) p.prof[blockIdx.x * 16 + (slot)] = (name)
 __device__ __forceinline__ long long prof_now_ns() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return static_cast<long long>(t); }
 #define PROF_STAMP(slot) p.prof[blockIdx.x * 16 + (slot)] = prof_now_ns()
+#if FP8BS_PROFILE >= 3   // per-K-block time line of CTA 0
 #define PROF_TRACE(ev, idx) do { if (blockIdx.x == 0 && (idx) < 128u) p.prof[4096 + (ev) * 128 + (idx)] = clock64(); } while (0)
+#else
+#define PROF_TRACE(ev, idx)
+#endif
 #define PROF_CLK0() const long long prof_c0__ = clock64()
 #define PROF_CLK1(slot) p.prof[blockIdx.x * 16 + (slot)] = clock64() - prof_c0__
 #else
