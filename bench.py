@@ -13,7 +13,7 @@ the GEMM path), and a shape's time is the max over ranks.  Rank 0 prints ONE JSO
              distinct buffer sets to exceed twice the L2 (so every launch reads its operands from HBM)
   e2e        the same geomean through the host-buffer entry point fp8bs_gemm_host: H2D of A, B and
              both scale arrays from pinned memory, the GEMM, D2H of C, inside the timed region
-  roofline   the dominant kernel (full-K, 256x256 CTA-pair tiles) on M=6144 N=4608 K=7168 against the tensor peak
+  roofline   the dominant kernel (the full-K kernel the dispatcher picks for M=6144 N=4608 K=7168) against the tensor peak
   cpu_baseline  the reference's CPU path (dequantise -> gemmCPU of utils.h:65-76 -> bf16) when
              oracle/_ref is present, else the CPU restatement in oracle/, on a bounded row sample
   m16384     aggregate TFLOP/s on the M=16384 variants of the nine (N, K) pairs, same partition
@@ -423,8 +423,10 @@ def run_gpu_arm(args, rank, world):
             traffic = json.load(fh).get("dram_bytes_per_launch")
     except Exception:
         pass
-    roofline = {"bound": "tensor", "kernel": "gemm_kernel<256,2,false> (256x256 CTA-pair tiles) on M=6144 N=4608 K=7168 "
-                                            "(1/%d column shard per GPU)" % world,
+    d_path, d_splits, d_tile = f.select_path(DOMINANT[0], plan_n_shards(DOMINANT[1], world)[0][1], DOMINANT[2])
+    d_name = ("256x256 CTA-pair tiles" if d_tile & f.TILE_PAIR else "128x%d tiles, one CTA each" % (d_tile & 0xFFF))
+    roofline = {"bound": "tensor", "kernel": "gemm_kernel (%s, %s) on M=6144 N=4608 K=7168 (1/%d column shard per GPU)"
+                                            % (d_name, "full K" if d_splits <= 1 else "split-K x%d" % d_splits, world),
                 "achieved": round(dom_tflops, 1), "peak": round(fp8_peak, 1), "unit": "TFLOP/s",
                 "frac": round(dom_tflops / fp8_peak, 4),
                 "peak_source": "2 x bf16_tflops (burst) of %s: fp8 issues at twice the bf16 rate; of %s" %
