@@ -159,7 +159,7 @@ constexpr int SM_TARGET = 148;   // B200; the dispatch is a pure function of the
 //   split-K inside a cluster: one CTA per (tile, K range); the number of clusters that fit on the GPU at once is
 //   cudaOccupancyMaxActiveClusters for this kernel's footprint (one CTA per SM), tabulated below for a B200;
 //   overhead 2 us (3 us for 256-wide tiles) + 0.5 us per split and 128 columns (shared-memory round trip, two
-//   cluster barriers).
+//   cluster barriers), paid again with 3 us of prologue by every further wave of clusters.
 static const int kMaxActiveClusters[9] = {0, 148, 74, 45, 33, 26, 22, 15, 15};
 static double config_cost(int M, int N, int K, int tile_n, int splits, int cg, int mode)
 {
@@ -171,7 +171,10 @@ static double config_cost(int M, int N, int K, int tile_n, int splits, int cg, i
     const double per_unit = (cg == 2) ? 2.0 : (tile_n == 256 ? 1.2 : 0.35);
     double cost = 3.5 + waves * (ceil_div(KB, splits) * per_kb + per_unit);
     if (splits > 1 && mode == 2) {
-        cost += (tile_n == 256 ? 3.0 : 2.0) + 0.5 * splits * (tile_n / 128);
+        // One CTA per (tile, K range), not persistent: a second wave of clusters pays the prologue and the
+        // reduction again, and nothing of it overlaps the wave before (measured on M = 16384 shapes).
+        const double overhead = (tile_n == 256 ? 3.0 : 2.0) + 0.5 * splits * (tile_n / 128);
+        cost += overhead + (waves - 1) * (overhead + 3.0);
     } else if (splits > 1) {
         const double overhead = 3.5 + 1.0 * splits * (tile_n / 128);
         cost += (waves > 1) ? 2.0 * overhead : overhead;
