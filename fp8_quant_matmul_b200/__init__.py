@@ -15,6 +15,7 @@ from .api import (  # noqa: F401
     PATH_MN_SMALL,
     TILE_PAIR,
     SPLIT_WORKSPACE,
+    STREAM_K,
     gemm,
     gemm_ref,
     gemm_mn_small_static,

@@ -111,7 +111,8 @@ static int device_setup(DeviceInfo** out)
         if ((rc = prepare_kernel<128, 1, 0>()) || (rc = prepare_kernel<256, 1, 0>()) ||
             (rc = prepare_kernel<256, 2, 0>()) || (rc = prepare_kernel<128, 1, 1>()) ||
             (rc = prepare_kernel<256, 1, 1>()) || (rc = prepare_kernel<256, 2, 1>()) ||
-            (rc = prepare_kernel<128, 1, 2>()) || (rc = prepare_kernel<256, 1, 2>())) {
+            (rc = prepare_kernel<128, 1, 2>()) || (rc = prepare_kernel<256, 1, 2>()) ||
+            (rc = prepare_kernel<128, 1, 3>()) || (rc = prepare_kernel<256, 1, 3>())) {
             d.status = rc;
             return rc;
         }
@@ -141,7 +142,9 @@ struct Config {
     int tile_n;   // 128 or 256
     int splits;   // 1 for mn_large
     int cg;       // 1: a CTA owns 128 rows of a tile; 2: a pair of CTAs owns 256 rows
-    int mode;     // 0 full K; 1 split-K reduced through a workspace; 2 split-K reduced inside a cluster
+    int mode;     // 0 full K; 1 split-K reduced through a workspace; 2 split-K reduced inside a cluster;
+                  // 3 stream-K: the K blocks of all tiles dealt out evenly over `ctas` CTAs
+    int ctas;     // mode 3 only
 };
 
 constexpr int MAX_CLUSTER_SPLITS = 6;   // clusters of 7 or 8 CTAs of this size fit only 15 at a time on a B200
@@ -149,6 +152,17 @@ constexpr int MAX_CLUSTER_SPLITS = 6;   // clusters of 7 or 8 CTAs of this size 
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
 constexpr int SM_TARGET = 148;   // B200; the dispatch is a pure function of the shape
+
+// Stream-K grid: every SM, but at least 4 K blocks per CTA.
+static int stream_k_ctas(int tiles, int KB)
+{
+    const long long total = static_cast<long long>(tiles) * KB;
+    long long g = total / 4;
+    if (g > SM_TARGET) g = SM_TARGET;
+    if (g < 1) g = 1;
+    return static_cast<int>(g);
+}
+
 
 // Estimated run time of a configuration in microseconds.  The constants come from a measured sweep of
 // every configuration over the 18 benchmark shapes on a B200 (power-capped, cold L2):
@@ -161,10 +175,23 @@ constexpr int SM_TARGET = 148;   // B200; the dispatch is a pure function of the
 //   overhead 2 us (3 us for 256-wide tiles) + 0.5 us per split and 128 columns (shared-memory round trip, two
 //   cluster barriers), paid again with 3 us of prologue by every further wave of clusters.
 static const int kMaxActiveClusters[9] = {0, 148, 74, 45, 33, 26, 22, 15, 15};
+// Stream-K hand-over per 128 columns of tile width: a CTA first leaves a partial tile in the workspace (its promotion
+// warps are busy with that while its MMA warp runs dry) and at the end reads its neighbours'; CTAs that run side by side
+// are also on tiles far apart and share less through L2.  Measured 6-11 us in total on the benchmark shapes, which
+// is why the estimate keeps stream-K for shapes with very few, very long tiles only.
+constexpr double STREAM_K_FIXUP_US = 6.0;
 static double config_cost(int M, int N, int K, int tile_n, int splits, int cg, int mode)
 {
     const int KB = K / 128;
     const int tiles = ceil_div(M, 128 * cg) * ceil_div(N, tile_n);
+    if (mode == 3) {
+        // every CTA: ceil(T / G) K blocks, its share of the tile switches, one partial-sum hand-over each way
+        const int g = stream_k_ctas(tiles, KB);
+        const long long total = static_cast<long long>(tiles) * KB;
+        const double kb_each = static_cast<double>((total + g - 1) / g);
+        const double per_kb3 = (tile_n == 256 ? 0.53 : 0.44), per_unit3 = (tile_n == 256 ? 1.2 : 0.35);
+        return 3.5 + kb_each * per_kb3 + (static_cast<double>(tiles) / g + 1.0) * per_unit3 + STREAM_K_FIXUP_US * (tile_n / 128);
+    }
     const int units = tiles * splits;
     const int waves = (mode == 2) ? ceil_div(tiles, kMaxActiveClusters[splits]) : ceil_div(units, SM_TARGET / cg);
     const double per_kb = (cg == 2) ? 0.60 : (tile_n == 256 ? 0.53 : 0.44);
@@ -189,9 +216,24 @@ static Config choose_config(int M, int N, int K, int path, int splits, int tile_
 {
     const int KB = K / 128;
     const bool force_ws = (tile_n & FP8BS_SPLIT_WORKSPACE) != 0;
-    const int want_tile = tile_n & ~FP8BS_SPLIT_WORKSPACE;
-    Config best{FP8BS_PATH_MN_LARGE, 128, 1, 1, 0};
+    const bool force_sk = (tile_n & FP8BS_STREAM_K) != 0;
+    const int want_tile = tile_n & ~(FP8BS_SPLIT_WORKSPACE | FP8BS_STREAM_K);
+    Config best{FP8BS_PATH_MN_LARGE, 128, 1, 1, 0, 0};
     double best_cost = 1e300;
+    // stream-K: a member of the mn_small family (it cuts K), chosen when it is asked for or when the caller left
+    // both path and splits open
+    if (force_sk || (path != FP8BS_PATH_MN_LARGE && splits == 0 && !force_ws)) {
+        for (int tn = 128; tn <= 256; tn += 128) {
+            if (want_tile && want_tile != tn) continue;
+            const int tiles = ceil_div(M, 128) * ceil_div(N, tn);
+            const double c = config_cost(M, N, K, tn, 1, 1, 3);
+            if (c < best_cost) {
+                best_cost = c;
+                best = Config{FP8BS_PATH_MN_SMALL, tn, 1, 1, 3, stream_k_ctas(tiles, KB)};
+            }
+        }
+        if (force_sk) return best;
+    }
     for (int cg = 1; cg <= 2; ++cg)
         for (int tn = 128; tn <= 256; tn += 128) {
             if (cg == 2 && tn != 256) continue;
@@ -205,7 +247,7 @@ static Config choose_config(int M, int N, int K, int path, int splits, int tile_
                     const double c = config_cost(M, N, K, tn, s, cg, mode);
                     if (c < best_cost) {
                         best_cost = c;
-                        best = Config{small ? FP8BS_PATH_MN_SMALL : FP8BS_PATH_MN_LARGE, tn, s, cg, mode};
+                        best = Config{small ? FP8BS_PATH_MN_SMALL : FP8BS_PATH_MN_LARGE, tn, s, cg, mode, 0};
                     }
                 }
             }
@@ -215,6 +257,8 @@ static Config choose_config(int M, int N, int K, int path, int splits, int tile_
 
 static size_t config_workspace(int M, int N, const Config& c)
 {
+    if (c.mode == 3)                                                 // flags + one partial tile per CTA
+        return COUNTER_BYTES + static_cast<size_t>(c.ctas) * (static_cast<size_t>(c.tile_n) * 128 * sizeof(float));
     if (c.path != FP8BS_PATH_MN_SMALL || c.mode != 1) return 0;      // only the workspace reduction needs scratch
     const size_t half_tiles = static_cast<size_t>(ceil_div(M, 128 * c.cg)) * c.cg * ceil_div(N, c.tile_n);
     return COUNTER_BYTES + half_tiles * c.splits * (static_cast<size_t>(c.tile_n) * 128 * sizeof(float));
@@ -235,8 +279,11 @@ static int check_args(int M, int N, int K, int n0, int n_total, int path, int sp
     if (splits < 0 || splits > K / 128 || splits > MAX_SPLITS) return FP8BS_ERR_ARG;
     if (path == FP8BS_PATH_MN_LARGE && splits > 1) return FP8BS_ERR_ARG;
     {
-        const int t = tile_n & ~FP8BS_SPLIT_WORKSPACE;
+        const int t = tile_n & ~(FP8BS_SPLIT_WORKSPACE | FP8BS_STREAM_K);
         if (t != 0 && t != 128 && t != 256 && t != (256 | FP8BS_TILE_PAIR)) return FP8BS_ERR_ARG;
+        if ((tile_n & FP8BS_STREAM_K) && ((tile_n & (FP8BS_TILE_PAIR | FP8BS_SPLIT_WORKSPACE)) || splits > 1 ||
+                                          path == FP8BS_PATH_MN_LARGE))
+            return FP8BS_ERR_ARG;
     }
     if (n0 < 0 || n0 % 64 != 0 || n_total < n0 + N) return FP8BS_ERR_ARG;
     return FP8BS_OK;
@@ -308,6 +355,7 @@ static int launch(const TensorMaps& tm, const GemmParams& p, int sm_count, cudaS
     const int units = p.m_tiles * p.n_tiles * p.splits;
     int groups = units < sm_count / CG ? units : sm_count / CG;    // tile walkers: CTAs or CTA pairs
     if (MODE == 2) groups = units;                                  // one CTA per (tile, K range); a cluster per tile
+    if (MODE == 3) groups = stream_k_ctas(p.m_tiles * p.n_tiles, p.K / 128);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(groups * CG), 1, 1);
     cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
@@ -332,6 +380,8 @@ static int launch(const TensorMaps& tm, const GemmParams& p, int sm_count, cudaS
 
 static int launch_config(const Config& c, const TensorMaps& tm, const GemmParams& p, int sm_count, cudaStream_t st)
 {
+    if (c.mode == 3)
+        return c.tile_n == 256 ? launch<256, 1, 3>(tm, p, sm_count, st) : launch<128, 1, 3>(tm, p, sm_count, st);
     if (c.mode == 2)
         return c.tile_n == 256 ? launch<256, 1, 2>(tm, p, sm_count, st) : launch<128, 1, 2>(tm, p, sm_count, st);
     if (c.mode == 1) {
@@ -354,13 +404,14 @@ static int gemm_impl(const void* A, const void* B, const float* a_scale, const f
     if ((reinterpret_cast<uintptr_t>(a_scale) & 15u) || (reinterpret_cast<uintptr_t>(b_scale) & 3u)) return FP8BS_ERR_ALIGN;
 
     Config cfg = choose_config(M, N, K, path, splits, tile_n);
-    if (cfg.mode == 1) {
+    if (cfg.mode == 1 || cfg.mode == 3) {
         const size_t need = config_workspace(M, N, cfg);
-        const size_t half_tiles = static_cast<size_t>(ceil_div(M, 128 * cfg.cg)) * cfg.cg * ceil_div(N, cfg.tile_n);
+        const size_t half_tiles = (cfg.mode == 3) ? static_cast<size_t>(cfg.ctas)
+            : static_cast<size_t>(ceil_div(M, 128 * cfg.cg)) * cfg.cg * ceil_div(N, cfg.tile_n);
         const bool fits = workspace && workspace_bytes >= need && half_tiles <= COUNTER_BYTES / sizeof(unsigned int) &&
                           (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0;
         if (!fits) {
-            if (path != FP8BS_PATH_AUTO) return FP8BS_ERR_WORKSPACE;
+            if (path != FP8BS_PATH_AUTO || (tile_n & (FP8BS_STREAM_K | FP8BS_SPLIT_WORKSPACE))) return FP8BS_ERR_WORKSPACE;
             cfg = choose_config(M, N, K, FP8BS_PATH_MN_LARGE, 1, tile_n);   // best full-K configuration
         }
     }
@@ -399,7 +450,7 @@ static int gemm_impl(const void* A, const void* B, const float* a_scale, const f
 #endif
     cudaStream_t st = static_cast<cudaStream_t>(stream);
 
-    if (cfg.mode == 1) {
+    if (cfg.mode == 1 || cfg.mode == 3) {
         p.counters = static_cast<unsigned int*>(workspace);
         p.partials = reinterpret_cast<float4*>(static_cast<char*>(workspace) + COUNTER_BYTES);
     }
@@ -609,7 +660,8 @@ int fp8bs_select_path(int M, int N, int K, int* splits, int* tile_n)
     if (rc) return rc;
     const Config c = choose_config(M, N, K, FP8BS_PATH_AUTO, 0, 0);
     if (splits) *splits = c.splits;
-    if (tile_n) *tile_n = c.tile_n | (c.cg == 2 ? FP8BS_TILE_PAIR : 0) | (c.mode == 1 ? FP8BS_SPLIT_WORKSPACE : 0);
+    if (tile_n) *tile_n = c.tile_n | (c.cg == 2 ? FP8BS_TILE_PAIR : 0) | (c.mode == 1 ? FP8BS_SPLIT_WORKSPACE : 0) |
+                          (c.mode == 3 ? FP8BS_STREAM_K : 0);
     return c.path;
 }
 

@@ -234,6 +234,7 @@ __device__ __forceinline__ void stage_and_store_64(const CUtensorMap* tmC, uint8
 // Self-test of the failure path: one warp waits, with a short limit, on a barrier that nothing ever arrives on.
 // The wait must give up, record DS_TIMEOUT_SELFTEST in the status word and the kernel must end normally.
 constexpr uint32_t DS_TIMEOUT_SELFTEST = 9;
+constexpr uint32_t DS_TIMEOUT_PEER_PARTIAL = 10;   // stream-K: another CTA's partial sums never arrived
 __global__ void wait_timeout_selftest_kernel(unsigned int* status, long long limit_cycles)
 {
     __shared__ uint64_t bar;
@@ -257,8 +258,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     constexpr int STAGES = Cfg::STAGES;
     constexpr int NBUF = Cfg::NBUF;
     constexpr int SRING = Cfg::SRING;
-    constexpr bool SPLITK = (MODE != 0);
+    constexpr bool SPLITK = (MODE == 1 || MODE == 2);   // K cut into p.splits equal ranges per tile
+    constexpr bool STREAMK = (MODE == 3);               // K blocks of all tiles dealt out evenly, see below
     static_assert(MODE != 2 || CG == 1, "the cluster reduction uses the cluster for the K splits");
+    static_assert(MODE != 3 || CG == 1, "stream-K is built for single-CTA tiles");
     // MODE 2: fp32 partial tile of this CTA, rows padded by 16 bytes so that a warp's 32 rows hit distinct banks
     constexpr int PART_PITCH = BN * 4 + 16;
     static_assert(MODE != 2 || 128 * PART_PITCH <= STAGES * Cfg::STAGE_BYTES, "partial tile must fit in the stage area");
@@ -334,17 +337,43 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     if (threadIdx.x == 0) { PROF_STAMP(9); }
 
     const int KB = p.K / Cfg::BK;
-    const int units = p.m_tiles * p.n_tiles * p.splits;
+    // MODE 3 (stream-K): the K blocks of all tiles form one line, tile after tile, and CTA c owns the piece
+    // [c * T / G, (c + 1) * T / G) of it, so every CTA does the same number of K blocks (+-1) whatever the tile count.
+    // A piece covers the end of one tile, whole tiles, and the beginning of one more.  A segment that starts inside
+    // a tile (only a CTA's first can) leaves its partial sums in workspace slot c and raises flag c; the segment
+    // that holds the tile's first K block adds the partials of the CTAs after it, in CTA (= K) order, and finishes
+    // the tile.  Those CTAs work on that tile first, so their flags are up long before they are looked at; nobody
+    // waits on a CTA that can itself be waiting (a first segment never waits).
+    long long sk_lo = 0, sk_hi = 0;
+    int sk_first = 0, sk_last = -1;
+    if constexpr (STREAMK) {
+        const long long T = static_cast<long long>(p.m_tiles) * p.n_tiles * KB;
+        sk_lo = blockIdx.x * T / gridDim.x;
+        sk_hi = (blockIdx.x + 1) * T / gridDim.x;
+        if (sk_hi > sk_lo) {
+            sk_first = static_cast<int>(sk_lo / KB);
+            sk_last = static_cast<int>((sk_hi - 1) / KB);
+        }
+    }
+    const int units = STREAMK ? (sk_last - sk_first + 1) : p.m_tiles * p.n_tiles * p.splits;
+    const int unit0 = STREAMK ? 0 : group_id;          // a CTA's (pair's) first work unit and its stride
+    const int unit_step = STREAMK ? 1 : num_groups;
 
     // unit -> (tile, split) -> (row of this CTA, first column, K-block range).  Tiles are numbered
     // m-fastest so CTAs that run side by side share the B slab through L2.
     auto decode = [&](int u, int& tile, int& m0, int& n0, int& kb0, int& kb1) {
-        const int split = SPLITK ? (u % p.splits) : 0;
-        tile = SPLITK ? (u / p.splits) : u;
+        if constexpr (STREAMK) {
+            tile = sk_first + u;
+            kb0 = (u == 0) ? static_cast<int>(sk_lo - static_cast<long long>(sk_first) * KB) : 0;
+            kb1 = (tile == sk_last) ? static_cast<int>(sk_hi - static_cast<long long>(sk_last) * KB) : KB;
+        } else {
+            const int split = SPLITK ? (u % p.splits) : 0;
+            tile = SPLITK ? (u / p.splits) : u;
+            kb0 = SPLITK ? (split * KB) / p.splits : 0;
+            kb1 = SPLITK ? ((split + 1) * KB) / p.splits : KB;
+        }
         m0 = (tile % p.m_tiles) * Cfg::TILE_M + static_cast<int>(rank) * Cfg::BM;
         n0 = (tile / p.m_tiles) * BN;
-        kb0 = SPLITK ? (split * KB) / p.splits : 0;
-        kb1 = SPLITK ? ((split + 1) * KB) / p.splits : KB;
     };
 
     if (warp < 4) {
@@ -354,7 +383,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             uint32_t it = 0;
             bool ok = true;
             PROF_DECL(w_empty);
-            for (int u = group_id; u < units && ok; u += num_groups) {
+            for (int u = unit0; u < units && ok; u += unit_step) {
                 int tile, m0, n0, kb0, kb1;
                 decode(u, tile, m0, n0, kb0, kb1);
                 const int nb0 = n0 + static_cast<int>(rank) * Cfg::B_COLS;    // first B column this CTA loads
@@ -403,7 +432,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 #endif
             uint32_t peer_base = 0;
             if constexpr (CG == 2) peer_base = ptx::mapa(bar_base, 1) - bar_base;   // offset to the peer's window
-            for (int u = group_id; u < units && ok; u += num_groups) {
+            for (int u = unit0; u < units && ok; u += unit_step) {
                 int tile, m0, n0, kb0, kb1;
                 decode(u, tile, m0, n0, kb0, kb1);
                 for (int kb = kb0; kb < kb1; ++kb, ++it, ++ait) {
@@ -459,7 +488,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             // ---------------------------------------------------- TMA producer: a_scale ----
             uint32_t sit = 0;
             bool ok = true;
-            for (int u = group_id; u < units && ok; u += num_groups) {
+            for (int u = unit0; u < units && ok; u += unit_step) {
                 int tile, m0, n0, kb0, kb1;
                 decode(u, tile, m0, n0, kb0, kb1);
                 for (int kb = kb0; kb < kb1; kb += Cfg::SGRP, ++sit) {
@@ -489,7 +518,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         uint32_t sgit = 0;                       // a_scale ring entries consumed so far
         bool ok = true;
         PROF_DECL(w_sfull); PROF_DECL(w_tfull); PROF_DECL(t_fma); PROF_DECL(t_epi);
-        for (int u = group_id; u < units; u += num_groups) {
+        for (int u = unit0; u < units; u += unit_step) {
             int tile, m0, n0, kb0, kb1;
             decode(u, tile, m0, n0, kb0, kb1);
             const int ncol0 = n0 + grp * Cfg::COLS;           // first local column of this thread
@@ -591,15 +620,93 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             if (pw == 0 && lane == 0) { PROF_STAMP(12); }
 #endif
 
-            if constexpr (!SPLITK) {
-                if (!ok) break;
-                // ---- epilogue: fp32 -> bf16 (round to nearest even), staged, TMA store ----
+            // ---- epilogue of a finished tile: fp32 -> bf16 (round to nearest even), staged, TMA store ----
+            auto store_tile = [&]() {
 #pragma unroll
                 for (int h = 0; h < Cfg::COLS / 64; ++h) {
                     const int box = (Cfg::NSTG == 2) ? h : 0;
                     stage_and_store_64<Cfg::NSTG - 1>(&tmC, my_stg + box * 4096, my_stg_addr + box * 4096, lane,
                                                       PackedCols{acc[2 * h], acc[2 * h + 1]}, ncol0 + h * 64,
                                                       m0 + quarter * 32, p.M, p.N);
+                }
+            };
+            if constexpr (MODE == 0) {
+                if (!ok) break;
+                store_tile();
+            } else if constexpr (MODE == 3) {
+                if (!ok) break;
+                // slot c of the workspace: [BN/4 column quads][128 rows] float4, a warp's 32 rows of one quad contiguous
+                auto slot_of = [&](int c) {
+                    return p.partials + (static_cast<size_t>(c) * (BN / 4) + grp * (Cfg::COLS / 4)) * 128 + row_in_tile;
+                };
+                if (kb0 > 0) {
+                    // ---- this segment starts inside the tile: publish its partial sums, raise the flag ----
+                    float4* part = slot_of(static_cast<int>(blockIdx.x));
+#pragma unroll
+                    for (int j = 0; j < Cfg::COLS / 4; ++j)
+                        part[static_cast<size_t>(j) * 128] =
+                            make_float4(f32x2_lo(acc[j / 8][(2 * j) % 16]), f32x2_hi(acc[j / 8][(2 * j) % 16]),
+                                        f32x2_lo(acc[j / 8][(2 * j + 1) % 16]), f32x2_hi(acc[j / 8][(2 * j + 1) % 16]));
+                    __threadfence();
+                    asm volatile("barrier.cta.sync.aligned 1, %0;" ::"n"(Cfg::PROMO_THREADS) : "memory");
+                    if (pw == 0 && lane == 0) {
+                        __threadfence();      // the whole CTA's partial sums (seen through the barrier) before the flag
+                        atomicExch(&p.counters[blockIdx.x], 1u);
+                    }
+                } else {
+                    if (kb1 < KB) {
+                        // ---- the tile's first K blocks are here, the rest was (or is being) done by the next CTAs ----
+                        int c_end = static_cast<int>(blockIdx.x) + 1;       // CTAs [blockIdx.x + 1, c_end) start inside this tile
+                        {
+                            const long long tile_end = static_cast<long long>(tile + 1) * KB;
+                            const long long T = static_cast<long long>(p.m_tiles) * p.n_tiles * KB;
+                            while (c_end < static_cast<int>(gridDim.x) && c_end * T / gridDim.x < tile_end) ++c_end;
+                        }
+                        for (int c = static_cast<int>(blockIdx.x) + 1; c < c_end; ++c) {
+                            if (pw == 0 && lane == 0) {
+                                // bounded wait for CTA c's flag
+                                const long long t0 = clock64();
+                                bool seen = false;
+                                while (!seen) {
+                                    unsigned int f;
+                                    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(f) : "l"(p.counters + c) : "memory");
+                                    seen = (f != 0u);
+                                    if (!seen) {
+                                        if (*abort_flag) break;
+                                        if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                                            *abort_flag = 1u;
+                                            atomicMax(p.status, DS_TIMEOUT_PEER_PARTIAL | (static_cast<uint32_t>(blockIdx.x) << 8));
+                                            break;
+                                        }
+                                        __nanosleep(100);
+                                    }
+                                }
+                                ctrl[2] = seen ? 1u : 0u;
+                            }
+                            asm volatile("barrier.cta.sync.aligned 1, %0;" ::"n"(Cfg::PROMO_THREADS) : "memory");
+                            if (!ctrl[2]) { ok = false; break; }
+                            const float4* ps = slot_of(c);
+#pragma unroll
+                            for (int h = 0; h < Cfg::COLS / 32; ++h) {      // 32 columns = one accumulator chunk per round
+                                float4 v[8];
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) v[j] = __ldcg(ps + static_cast<size_t>(h * 8 + j) * 128);
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) {
+                                    // columns 32h + 4j .. +3 are the pairs 2j and 2j + 1 of chunk h
+                                    unsigned long long& a0 = acc[h][2 * j];
+                                    unsigned long long& a1 = acc[h][2 * j + 1];
+                                    a0 = pack_f32x2(f32x2_lo(a0) + v[j].x, f32x2_hi(a0) + v[j].y);
+                                    a1 = pack_f32x2(f32x2_lo(a1) + v[j].z, f32x2_hi(a1) + v[j].w);
+                                }
+                            }
+                            // every thread has read slot c: re-arm its flag for the next call
+                            asm volatile("barrier.cta.sync.aligned 1, %0;" ::"n"(Cfg::PROMO_THREADS) : "memory");
+                            if (pw == 0 && lane == 0) p.counters[c] = 0u;
+                        }
+                        if (!ok) break;
+                    }
+                    store_tile();
                 }
             } else if constexpr (MODE == 2) {
                 // ---- split-K through the cluster: leave this K range's partial tile in shared memory ----

@@ -54,10 +54,16 @@ extern "C" {
 /* tile_n values: 0 = let the library choose; 128 or 256 = tile width with one CTA per 128-row tile;
  * 256 | FP8BS_TILE_PAIR = a 256 x 256 tile owned by a pair of CTAs (tcgen05 cta_group::2). */
 #define FP8BS_TILE_PAIR      0x1000
-/* Split-K partial sums are normally reduced inside a thread-block cluster through shared memory (2..8 splits, one
+/* Split-K partial sums are normally reduced inside a thread-block cluster through shared memory (2..6 splits, one
  * CTA per tile): no workspace is needed then.  OR this flag into tile_n to reduce through the workspace instead
- * (always used for more than 8 splits and for pair tiles). */
+ * (always used for more than 6 splits and for pair tiles). */
 #define FP8BS_SPLIT_WORKSPACE 0x2000
+/* Stream-K: the 128-K blocks of all tiles are dealt out evenly over the SMs, so the run time does not jump with the
+ * tile count; a tile whose blocks fall to two or more CTAs is finished by the CTA that holds its first block, from
+ * partial sums the others leave in the workspace (added in K order: results do not depend on timing).  Chosen by the
+ * library when path and splits are left open and it is estimated fastest; OR this flag into tile_n (128 or 256, or 0)
+ * to force it.  Needs the workspace (fp8bs_workspace_bytes_ex), splits must be 0 or 1. */
+#define FP8BS_STREAM_K       0x4000
 
 /* ---- the operator ---------------------------------------------------------------- */
 

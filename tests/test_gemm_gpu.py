@@ -52,12 +52,15 @@ FORCED = [
     dict(path=f.PATH_MN_SMALL, splits=2, tile_n=256 | f.TILE_PAIR),
     dict(path=f.PATH_MN_SMALL, splits=2, tile_n=128 | f.SPLIT_WORKSPACE),  # split-K reduced through the workspace
     dict(path=f.PATH_MN_SMALL, splits=2, tile_n=256 | f.SPLIT_WORKSPACE),
+    dict(path=f.PATH_MN_SMALL, splits=1, tile_n=128 | f.STREAM_K),         # K blocks of all tiles dealt out over the SMs
+    dict(path=f.PATH_MN_SMALL, splits=1, tile_n=256 | f.STREAM_K),
 ]
 
 
 def ids(cfgs):
     return ["p%d-s%d-t%d%s%s" % (c["path"], c["splits"], c["tile_n"] & 0xFFF, "pair" if c["tile_n"] & f.TILE_PAIR else "",
-                                 "ws" if c["tile_n"] & f.SPLIT_WORKSPACE else "") for c in cfgs]
+                                 "ws" if c["tile_n"] & f.SPLIT_WORKSPACE else ("sk" if c["tile_n"] & f.STREAM_K else ""))
+            for c in cfgs]
 
 
 # ------------------------------------------------------------------ known answers ----------
@@ -174,9 +177,13 @@ def test_both_kernels_forced_on_named_configs(shape):
 @pytest.mark.parametrize("shape,splits,tile_n", [((1024, 576, 7168), 7, 128), ((6144, 512, 7168), 6, 128),
                                                  ((6144, 512, 7168), 3, 256 | 0x1000), ((6144, 512, 7168), 7, 256),
                                                  ((1024, 576, 7168), 7, 128 | 0x2000), ((6144, 512, 7168), 6, 128 | 0x2000),
-                                                 ((6144, 512, 7168), 9, 128), ((6144, 512, 7168), 7, 256 | 0x2000)],
+                                                 ((6144, 512, 7168), 9, 128), ((6144, 512, 7168), 7, 256 | 0x2000),
+                                                 ((1024, 576, 7168), 1, 128 | 0x4000), ((6144, 512, 7168), 1, 256 | 0x4000),
+                                                 ((1024, 1536, 7168), 1, 256 | 0x4000), ((1024, 7168, 2304), 1, 256 | 0x4000)],
                          ids=["1024x576-s7-t128", "6144x512-s6-t128", "6144x512-s3-pair", "6144x512-s7-t256",
-                              "1024x576-s7-t128-ws", "6144x512-s6-t128-ws", "6144x512-s9-t128-ws", "6144x512-s7-t256-ws"])
+                              "1024x576-s7-t128-ws", "6144x512-s6-t128-ws", "6144x512-s9-t128-ws", "6144x512-s7-t256-ws",
+                              "1024x576-t128-streamk", "6144x512-t256-streamk", "1024x1536-t256-streamk",
+                              "1024x7168x2304-t256-streamk"])
 def test_split_k_is_bit_deterministic(shape, splits, tile_n):
     # several work units per CTA; the workspace is poisoned with NaN before every run so that a partial sum
     # read before it was written, or left over from another run, cannot go unnoticed

@@ -43,11 +43,14 @@ def test_dispatch_policy_on_the_18_shapes():
     for (M, N, K) in f.SHAPES_18:
         path, splits, tile_n = f.select_path(M, N, K)
         assert path in (f.PATH_MN_LARGE, f.PATH_MN_SMALL)
-        assert (tile_n & ~f.SPLIT_WORKSPACE) in (128, 256, 256 | f.TILE_PAIR)
+        assert (tile_n & ~(f.SPLIT_WORKSPACE | f.STREAM_K)) in (128, 256, 256 | f.TILE_PAIR)
         assert 1 <= splits <= K // 128
-        assert (path == f.PATH_MN_SMALL) == (splits > 1)
+        # the mn_small family cuts K: into `splits` ranges per tile, or (stream-K) evenly over the SMs
+        assert (path == f.PATH_MN_SMALL) == (splits > 1 or bool(tile_n & f.STREAM_K))
         ws = f.workspace_bytes(M, N, K)
-        assert (ws > 0) == bool(tile_n & f.SPLIT_WORKSPACE)        # cluster reductions need no workspace
+        assert (ws > 0) == bool(tile_n & (f.SPLIT_WORKSPACE | f.STREAM_K))   # cluster reductions need no workspace
+        if tile_n & f.STREAM_K:
+            assert ws == 65536 + min(148, (M // 128) * -(-N // (tile_n & 0xFFF)) * (K // 128) // 4) * (tile_n & 0xFFF) * 128 * 4
     assert f.select_path(6144, 4608, 7168)[0] == f.PATH_MN_LARGE
     assert f.select_path(1024, 512, 7168)[0] == f.PATH_MN_SMALL
     assert f.select_path(1024, 576, 7168)[0] == f.PATH_MN_SMALL
