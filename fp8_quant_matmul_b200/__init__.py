@@ -19,6 +19,7 @@ from .api import (  # noqa: F401
     gemm,
     gemm_ref,
     gemm_mn_small_static,
+    gemm_scatter,
     STATIC_SCRATCH_BYTES,
     gemmGPU,
     quantize_rowwise,

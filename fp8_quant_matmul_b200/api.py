@@ -37,6 +37,7 @@ _SIGS = {
     "fp8bs_gemm_mn_small": (_c.c_int, [_c.c_void_p] * 5 + [_c.c_int] * 4 + [_c.c_void_p, _c.c_size_t, _c.c_void_p]),
     "fp8bs_gemm_mn_small_static": (_c.c_int, [_c.c_void_p] * 5 + [_c.c_int] * 4 + [_c.c_void_p]),
     "fp8bs_gemm_ex": (_c.c_int, [_c.c_void_p] * 5 + [_c.c_int] * 8 + [_c.c_void_p, _c.c_size_t, _c.c_void_p]),
+    "fp8bs_gemm_scatter": (_c.c_int, [_c.c_void_p] * 4 + [_c.POINTER(_c.c_void_p)] + [_c.c_int] * 6 + [_c.c_void_p]),
     "fp8bs_gemm_ref": (_c.c_int, [_c.c_void_p] * 5 + [_c.c_int] * 3 + [_c.c_void_p]),
     "fp8bs_select_path": (_c.c_int, [_c.c_int] * 3 + [_c.POINTER(_c.c_int)] * 2),
     "fp8bs_workspace_bytes": (_c.c_size_t, [_c.c_int] * 3),
@@ -226,6 +227,21 @@ def gemm(A, B, a_scale, b_scale, C=None, M=None, N=None, K=None, path=PATH_AUTO,
                              M, N, K, n0, n_total, path, splits, tile_n, ws_ptr, ws_bytes, stream)
     _check(rc, "fp8bs_gemm_ex")
     return C
+
+
+def gemm_scatter(A, B, a_scale, b_scale, dests, M, N, K, n0, n_total, stream=None):
+    """N-sharded GEMM with the distribution of C fused into the epilogue: computes columns [n0, n0 + N) of an
+    n_total-wide C and stores them into every buffer of `dests` (device pointers as ints, or torch tensors of shape
+    [M, n_total] bf16): this GPU's own C and the peer-mapped C of the other GPUs."""
+    import torch
+    ptrs = [d.data_ptr() if hasattr(d, "data_ptr") else int(d) for d in dests]
+    arr = (_c.c_void_p * len(ptrs))(*ptrs)
+    if stream is None:
+        stream = torch.cuda.current_stream(A.device).cuda_stream
+    with torch.cuda.device(A.device):
+        rc = lib().fp8bs_gemm_scatter(A.data_ptr(), B.data_ptr(), a_scale.data_ptr(), b_scale.data_ptr(), arr, len(ptrs),
+                                      M, N, K, n0, n_total, stream)
+    _check(rc, "fp8bs_gemm_scatter")
 
 
 STATIC_SCRATCH_BYTES = (32 << 20) + 65536

@@ -328,10 +328,11 @@ static int encode_scale_map(CUtensorMap* tm, const float* base, int M, int KB)
 }
 
 // C as a 2-D bf16 tensor {N, M} (row-major M x N); a store box is 64 columns x 32 rows, 128-byte swizzled.
-static int encode_c_map(CUtensorMap* tm, void* base, int M, int N)
+static int encode_c_map(CUtensorMap* tm, void* base, int M, int N, int ld)
 {
+    // `base` is the first element of the M x N window this call writes; `ld` is the row pitch of the buffer in elements
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(M)};
-    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(N) * 2};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
     const cuuint32_t box[2] = {64u, 32u};
     const cuuint32_t estr[2] = {1u, 1u};
     const CUresult r = g_encode_tiled(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, estr,
@@ -345,7 +346,8 @@ static int encode_c_map(CUtensorMap* tm, void* base, int M, int N)
 }
 
 struct TensorMaps {
-    CUtensorMap A, B, As, C;
+    CUtensorMap A, B, As;
+    CMaps C;
 };
 
 template <int BN, int CG, int MODE>
@@ -392,10 +394,21 @@ static int launch_config(const Config& c, const TensorMaps& tm, const GemmParams
     return c.tile_n == 256 ? launch<256, 1, 0>(tm, p, sm_count, st) : launch<128, 1, 0>(tm, p, sm_count, st);
 }
 
+// `dests` / `n_dest`: null / 0 for the ordinary call (C is an M x N buffer of its own); otherwise n_dest buffers of
+// n_total columns each, all of which receive this call's columns [n0, n0 + N) (C is ignored).
 static int gemm_impl(const void* A, const void* B, const float* a_scale, const float* b_scale, void* C, int M,
                      int N, int K, int n0, int n_total, int path, int splits, int tile_n, void* workspace,
-                     size_t workspace_bytes, void* stream)
+                     size_t workspace_bytes, void* stream, void* const* dests = nullptr, int n_dest = 0)
 {
+    if (dests) {
+        if (n_dest < 1 || n_dest > MAX_DEST) return FP8BS_ERR_ARG;
+        for (int d = 0; d < n_dest; ++d) {
+            if (!dests[d]) return FP8BS_ERR_NULL;
+            if (reinterpret_cast<uintptr_t>(dests[d]) & 15u) return FP8BS_ERR_ALIGN;
+        }
+        if (n_total % 8 != 0) return FP8BS_ERR_ALIGN;       // row pitch of the destinations: a multiple of 16 bytes
+        C = dests[0];
+    }
     if (!A || !B || !a_scale || !b_scale || !C) return FP8BS_ERR_NULL;
     int rc = check_args(M, N, K, n0, n_total, path, splits, tile_n);
     if (rc) return rc;
@@ -404,6 +417,7 @@ static int gemm_impl(const void* A, const void* B, const float* a_scale, const f
     if ((reinterpret_cast<uintptr_t>(a_scale) & 15u) || (reinterpret_cast<uintptr_t>(b_scale) & 3u)) return FP8BS_ERR_ALIGN;
 
     Config cfg = choose_config(M, N, K, path, splits, tile_n);
+    if (dests && cfg.mode == 2) return FP8BS_ERR_ARG;       // the cluster reduction stores C itself, to one buffer
     if (cfg.mode == 1 || cfg.mode == 3) {
         const size_t need = config_workspace(M, N, cfg);
         const size_t half_tiles = (cfg.mode == 3) ? static_cast<size_t>(cfg.ctas)
@@ -420,11 +434,14 @@ static int gemm_impl(const void* A, const void* B, const float* a_scale, const f
     rc = device_setup(&dev);
     if (rc) return rc;
 
-    TensorMaps tm;
+    TensorMaps tm{};
     if ((rc = encode_operand_map(&tm.A, A, M, K))) return rc;
     if ((rc = encode_operand_map(&tm.B, B, N, K))) return rc;
     if ((rc = encode_scale_map(&tm.As, a_scale, M, K / 128))) return rc;
-    if ((rc = encode_c_map(&tm.C, C, M, N))) return rc;
+    if (dests) {
+        for (int d = 0; d < n_dest; ++d)
+            if ((rc = encode_c_map(&tm.C.m[d], static_cast<__nv_bfloat16*>(dests[d]) + n0, M, N, n_total))) return rc;
+    } else if ((rc = encode_c_map(&tm.C.m[0], C, M, N, N))) return rc;
 
     GemmParams p;
     p.b_scale = b_scale;
@@ -438,6 +455,7 @@ static int gemm_impl(const void* A, const void* B, const float* a_scale, const f
     p.m_tiles = ceil_div(M, 128 * cfg.cg);
     p.n_tiles = ceil_div(N, cfg.tile_n);
     p.splits = cfg.splits;
+    p.n_dest = dests ? n_dest : 1;
     p.elem_scale = 1.0f;
 #ifdef FP8BS_PROFILE
     {
@@ -604,6 +622,14 @@ int fp8bs_gemm_ex(const void* A, const void* B, const float* a_scale, const floa
 {
     return gemm_impl(A, B, a_scale, b_scale, C, M, N, K, n0, n_total, path, splits, tile_n, workspace,
                      workspace_bytes, stream);
+}
+
+int fp8bs_gemm_scatter(const void* A, const void* B, const float* a_scale, const float* b_scale, void* const* C_dest,
+                       int n_dest, int M, int N, int K, int n0, int n_total, void* stream)
+{
+    if (!C_dest) return FP8BS_ERR_NULL;
+    return gemm_impl(A, B, a_scale, b_scale, nullptr, M, N, K, n0, n_total, FP8BS_PATH_MN_LARGE, 1, 0, nullptr, 0,
+                     stream, C_dest, n_dest);
 }
 
 // Split-K GEMM for callers that must not allocate.  The scratch is the file-scope device array above: in host code

@@ -65,6 +65,13 @@ enum : uint32_t {
     DS_TIMEOUT_SCALE_FULL = 6,   // promotion warps waited for a_scale
 };
 
+// Where a finished C tile goes: the caller's C, and for the fused distribution (fp8bs_gemm_scatter) the same window
+// of up to MAX_DEST - 1 further buffers, e.g. the peer-mapped C of the other GPUs of an N-sharded GEMM.
+constexpr int MAX_DEST = 8;
+struct CMaps {
+    CUtensorMap m[MAX_DEST];
+};
+
 struct GemmParams {
     const float* b_scale;    // [sn, K/128], nb contiguous          (check.cu:46)
     __nv_bfloat16* C;        // M x N row-major                     (check.cu:48)
@@ -75,6 +82,7 @@ struct GemmParams {
     int n_off;               // global column index of local column 0 (N-sharded calls), else 0
     int sn;                  // rows of b_scale = ceil(N_total / 128)  (check.cu:36)
     int m_tiles, n_tiles, splits;
+    int n_dest;              // number of valid entries of the CMaps argument (1 = only the caller's C)
     float elem_scale;        // folded into b_scale: 1 for e4m3fn bytes
 #ifdef FP8BS_PROFILE
     long long* prof;         // per CTA: 8 cycle counters (profiling builds only)
@@ -208,8 +216,8 @@ struct FloatCols {
 // PENDING: how many of this thread's most recent stores may still be reading shared memory (1 when the warp
 // alternates between two boxes: only the store before the last one used this box).
 template <int PENDING, class Cols>
-__device__ __forceinline__ void stage_and_store_64(const CUtensorMap* tmC, uint8_t* stg, uint32_t stg_addr, int lane,
-                                                   const Cols cols, int col, int row0, int M, int N)
+__device__ __forceinline__ void stage_and_store_64(const CUtensorMap* tmC, int n_dest, uint8_t* stg, uint32_t stg_addr,
+                                                   int lane, const Cols cols, int col, int row0, int M, int N)
 {
     if (lane == 0) ptx::tma_store_wait_read<PENDING>();      // the previous store out of this box has read it
     __syncwarp();
@@ -226,7 +234,8 @@ __device__ __forceinline__ void stage_and_store_64(const CUtensorMap* tmC, uint8
     ptx::fence_proxy_async_smem();
     __syncwarp();
     if (lane == 0 && col < N && row0 < M) {
-        ptx::tma_store_2d(tmC, stg_addr, col, row0);   // rows >= M and columns >= N are clipped by the hardware
+        // rows >= M and columns >= N are clipped by the hardware; one bulk group covers every destination's copy
+        for (int d = 0; d < n_dest; ++d) ptx::tma_store_2d(tmC + d, stg_addr, col, row0);
         ptx::tma_store_commit();
     }
 }
@@ -252,7 +261,7 @@ __global__ void wait_timeout_selftest_kernel(unsigned int* status, long long lim
 template <int BN, int CG, int MODE>
 __global__ void __launch_bounds__(TileCfg<BN, CG>::THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-            const __grid_constant__ CUtensorMap tmAs, const __grid_constant__ CUtensorMap tmC, const GemmParams p)
+            const __grid_constant__ CUtensorMap tmAs, const __grid_constant__ CMaps cmaps, const GemmParams p)
 {
     using Cfg = TileCfg<BN, CG>;
     constexpr int STAGES = Cfg::STAGES;
@@ -298,7 +307,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         ptx::prefetch_tensormap(&tmA);
         ptx::prefetch_tensormap(&tmB);
         ptx::prefetch_tensormap(&tmAs);
-        ptx::prefetch_tensormap(&tmC);
+        for (int d = 0; d < p.n_dest; ++d) ptx::prefetch_tensormap(&cmaps.m[d]);
         for (int s = 0; s < STAGES; ++s) {
             ptx::mbar_init(full_bar(s), 1);
             ptx::mbar_init(empty_bar(s), 1);
@@ -625,7 +634,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 #pragma unroll
                 for (int h = 0; h < Cfg::COLS / 64; ++h) {
                     const int box = (Cfg::NSTG == 2) ? h : 0;
-                    stage_and_store_64<Cfg::NSTG - 1>(&tmC, my_stg + box * 4096, my_stg_addr + box * 4096, lane,
+                    stage_and_store_64<Cfg::NSTG - 1>(cmaps.m, p.n_dest, my_stg + box * 4096, my_stg_addr + box * 4096, lane,
                                                       PackedCols{acc[2 * h], acc[2 * h + 1]}, ncol0 + h * 64,
                                                       m0 + quarter * 32, p.M, p.N);
                 }
@@ -779,7 +788,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                                 sum[4 * j + 3] += v.w;
                             }
                         }
-                        stage_and_store_64<0>(&tmC, my_stg, my_stg_addr, lane, FloatCols{sum}, ncol0 + h * 64, m0 + quarter * 32, p.M, p.N);
+                        stage_and_store_64<0>(cmaps.m, p.n_dest, my_stg, my_stg_addr, lane, FloatCols{sum}, ncol0 + h * 64, m0 + quarter * 32, p.M, p.N);
                     }
                 }
             }

@@ -104,6 +104,18 @@ int fp8bs_gemm_mn_small(const void* A, const void* B, const float* a_scale, cons
 int fp8bs_gemm_mn_small_static(const void* A, const void* B, const float* a_scale, const float* b_scale,
                                void* C, int M, int N, int K, int splits, void* stream);
 
+/* Fused distribution of C for an N-sharded GEMM (no counterpart in the reference, which runs on one GPU).
+ * Computes the columns [n0, n0 + N) of a C that is n_total columns wide, exactly as fp8bs_gemm_ex does (B holds only
+ * those N columns, b_scale is the whole [ceil(n_total/128), K/128] array), and stores every finished tile into the
+ * same window of each of the n_dest (1..8) row-major M x n_total bf16 buffers in C_dest: TMA stores straight out of the
+ * epilogue, one per destination, instead of a separate all-gather and re-layout pass.  The pointers must be usable
+ * from this device: the GPU's own buffer and peer-mapped buffers of other GPUs (cudaIpc / symmetric memory).  Runs the
+ * full-K kernel.  The call returns when the launch is queued; a destination is complete when its owner has
+ * synchronised with every writer (a barrier between the ranks after the stream has drained).  C_dest is a host array.
+ * Needs 16-byte aligned buffers and n_total % 8 == 0, besides the rules of fp8bs_gemm_ex. */
+int fp8bs_gemm_scatter(const void* A, const void* B, const float* a_scale, const float* b_scale,
+                       void* const* C_dest, int n_dest, int M, int N, int K, int n0, int n_total, void* stream);
+
 /* Everything explicit.  For an N-shard of a wider problem (multi-GPU partition by columns):
  * B and C hold columns [n0, n0+N) of an n_total-column problem, b_scale is the FULL
  * [ceil(n_total/128), K/128] array, n0 % 64 == 0.  The plain operator is n0 = 0,

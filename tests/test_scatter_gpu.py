@@ -1,0 +1,112 @@
+"""Fused distribution of C (fp8bs_gemm_scatter): an N-sharded GEMM whose epilogue stores every finished tile into the
+full-width C of several destinations.  On one GPU the destinations are separate local buffers; with two or more
+GPUs the test runs one process per GPU and the destinations are the ranks' peer-mapped buffers."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import fp8_quant_matmul_b200 as f
+from fp8_quant_matmul_b200.shard import plan_n_shards
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+import helpers as h  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+
+def dev():
+    return torch.device("cuda:0")
+
+
+@pytest.mark.parametrize("shape,shards,ndest", [((256, 512, 512), 2, 2), ((384, 1152, 1024), 3, 3), ((1024, 576, 1024), 4, 8),
+                                                ((144, 320, 384), 2, 1)],
+                         ids=["256x512-2shards", "384x1152-3shards", "1024x576-4shards-8dest", "ragged-1dest"])
+def test_every_destination_receives_every_shard(shape, shards, ndest):
+    M, N, K = shape
+    A, B, a_s, b_s = h.make_inputs(M, N, K, seed=41)
+    ref = h.oracle_gemm(A, B, a_s, b_s, M, N, K)
+    dA = torch.from_numpy(A).to(dev())
+    dAs, dBs = torch.from_numpy(a_s).to(dev()), torch.from_numpy(b_s).to(dev())
+    dests = [torch.full((M + 2, N), float("nan"), dtype=torch.bfloat16, device=dev()) for _ in range(ndest)]
+    Bm = B.reshape(K, N)
+    for (n0, nl) in plan_n_shards(N, shards):
+        dB = torch.from_numpy(np.ascontiguousarray(Bm[:, n0:n0 + nl]).ravel()).to(dev())
+        f.gemm_scatter(dA, dB, dAs, dBs, [d[1:M + 1] for d in dests], M, nl, K, n0, N)
+    f.last_device_status()
+    for d in dests:
+        bits = d.view(torch.int16).cpu().numpy().view(np.uint16)
+        assert np.isnan(h.bf16_bits_to_f32(bits[0])).all() and np.isnan(h.bf16_bits_to_f32(bits[M + 1])).all()   # guard rows
+        bad, first, maxerr = h.mismatches(ref, bits[1:M + 1])
+        assert bad == 0, "%d mismatches, first %d, max err %g" % (bad, first, maxerr)
+
+
+def test_scatter_argument_errors():
+    M, N, K = 128, 256, 256
+    z8 = torch.zeros(M * K, dtype=torch.uint8, device=dev())
+    zb = torch.zeros(N * K, dtype=torch.uint8, device=dev())
+    s1 = torch.ones(M * 2, dtype=torch.float32, device=dev())
+    s2 = torch.ones(2 * 2, dtype=torch.float32, device=dev())
+    C = torch.zeros((M, N), dtype=torch.bfloat16, device=dev())
+    with pytest.raises(f.Fp8bsError) as e:
+        f.gemm_scatter(z8, zb, s1, s2, [C] * 9, M, N, K, 0, N)        # more than 8 destinations
+    assert e.value.code == -5
+    with pytest.raises(f.Fp8bsError) as e:
+        f.gemm_scatter(z8, zb, s1, s2, [C.data_ptr() + 2], M, N, K, 0, N)   # misaligned destination
+    assert e.value.code == -3
+    with pytest.raises(f.Fp8bsError) as e:
+        f.gemm_scatter(z8, zb, s1, s2, [C], M, 128, K, 32, N)           # shard boundary not on 64 columns
+    assert e.value.code == -5
+
+
+def _rank_main(rank, world, port, q):
+    try:
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        torch.cuda.set_device(rank)
+        d = torch.device("cuda", rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=d)
+        M, N, K = 512, 1024, 1024
+        A, B, a_s, b_s = h.make_inputs(M, N, K, seed=43)
+        n0, nl = plan_n_shards(N, world)[rank]
+        Cfull = symm.empty((M, N), dtype=torch.bfloat16, device=d)
+        Cfull.fill_(float("nan"))
+        hdl = symm.rendezvous(Cfull, dist.group.WORLD.group_name)
+        dist.barrier()
+        torch.cuda.synchronize()
+        dA = torch.from_numpy(A).to(d)
+        dB = torch.from_numpy(np.ascontiguousarray(B.reshape(K, N)[:, n0:n0 + nl]).ravel()).to(d)
+        f.gemm_scatter(dA, dB, torch.from_numpy(a_s).to(d), torch.from_numpy(b_s).to(d),
+                       [int(p) for p in hdl.buffer_ptrs], M, nl, K, n0, N)
+        torch.cuda.synchronize()
+        dist.barrier()                       # every rank has written its columns into every C
+        torch.cuda.synchronize()
+        f.last_device_status()
+        bits = Cfull.view(torch.int16).cpu().numpy().view(np.uint16)
+        bad, first, maxerr = h.mismatches(h.oracle_gemm(A, B, a_s, b_s, M, N, K), bits)
+        q.put((rank, bad, ""))
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception as exc:          # report instead of hanging the parent
+        import traceback
+        q.put((rank, -1, traceback.format_exc()[-1500:]))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpus_write_each_others_c():
+    import torch.multiprocessing as mp
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + os.getpid() % 2000
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, bad, msg in results:
+        assert bad == 0, "rank %d: %s %s" % (rank, bad, msg)
