@@ -399,6 +399,52 @@ def run_gpu_arm(args, rank, world):
         allgather = {"shape": "C 16384 x 7168 bf16 in %d column slabs" % world, "us": round(us, 1),
                      "bus_GBps": round(out.numel() * 2 * (world - 1) / world / us / 1e3, 1)}
 
+    # ---- distribution of C fused into the GEMM epilogue (fp8bs_gemm_scatter) against GEMM + all-gather ----
+    fused = None
+    if dist is not None:
+        try:
+            import torch.distributed._symmetric_memory as symm
+            M, N, K = 16384, 7168, 2304
+            n0, nl = plan_n_shards(N, world)[rank]
+            dA = torch.from_numpy(f.gen_normal_e4m3(M * K, 9001)).to(dev)
+            dB = torch.from_numpy(f.gen_normal_e4m3(nl * K, 9002 + rank)).to(dev)
+            dAs = torch.from_numpy(f.gen_uniform_f32(M * (K // 128), 9003, 0.01, 1.0)).to(dev)
+            dBs = torch.from_numpy(f.gen_uniform_f32(((N + 127) // 128) * (K // 128), 9004, 0.01, 1.0)).to(dev)
+            c_full = symm.empty((M, N), dtype=torch.bfloat16, device=dev)
+            hdl = symm.rendezvous(c_full, dist.group.WORLD.group_name)
+            ptrs = [int(x) for x in hdl.buffer_ptrs]
+            c_own = torch.empty((M, nl), dtype=torch.bfloat16, device=dev)
+            gathered = torch.empty((world, M, nl), dtype=torch.bfloat16, device=dev)
+
+            def timed(fn, reps=10):
+                for _ in range(3):
+                    fn()
+                barrier()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(reps):
+                    fn()
+                e1.record()
+                barrier()
+                return max_over_ranks([e0.elapsed_time(e1) * 1e3 / reps])[0]
+
+            def separate():
+                f.gemm(dA, dB, dAs, dBs, c_own, M, nl, K, n0=n0, n_total=N, path=f.PATH_MN_LARGE)
+                dist.all_gather_into_tensor(gathered, c_own)
+
+            t_gemm = timed(lambda: f.gemm(dA, dB, dAs, dBs, c_own, M, nl, K, n0=n0, n_total=N, path=f.PATH_MN_LARGE))
+            t_sep = timed(separate)
+            t_fused = timed(lambda: f.gemm_scatter(dA, dB, dAs, dBs, ptrs, M, nl, K, n0, N))
+            f.last_device_status()
+            fused = {"shape": "M=16384 N=7168 K=2304, C row-major on every GPU", "gemm_only_us": round(t_gemm, 1),
+                     "gemm_then_nccl_all_gather_us": round(t_sep, 1), "gemm_with_fused_distribution_us": round(t_fused, 1),
+                     "note": "all-gather leaves [rank][M][N/ranks] slabs that still need a re-layout pass; the fused "
+                             "epilogue writes row-major M x N directly; peer bytes per GPU %.0f MB" %
+                             ((world - 1) * M * nl * 2 / 1e6)}
+            del c_full, hdl
+        except Exception as exc:                                   # symmetric memory unavailable on this box
+            fused = {"unavailable": str(exc)[:300]}
+
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -452,6 +498,7 @@ def run_gpu_arm(args, rank, world):
         "shapes": shapes_out,
         "m16384": {"aggregate_tflops": round(agg_flops / agg_us / 1e6, 1), "per_shape": m16},
         "allgather_c": allgather,
+        "fused_c_distribution": fused,
     }
     emit(line)
     if dist is not None:
