@@ -438,6 +438,9 @@ def run_gpu_arm(args, rank, world):
             f.last_device_status()
             fused = {"shape": "M=16384 N=7168 K=2304, C row-major on every GPU", "gemm_only_us": round(t_gemm, 1),
                      "gemm_then_nccl_all_gather_us": round(t_sep, 1), "gemm_with_fused_distribution_us": round(t_fused, 1),
+                     "roofline": {"bound": "slower of the GEMM alone and the peer bytes over one NVLink direction (770 GB/s measured peer copy)",
+                                  "target_us": round(max(t_gemm, (world - 1) * M * nl * 2 / 770e3), 1),
+                                  "frac": round(max(t_gemm, (world - 1) * M * nl * 2 / 770e3) / t_fused, 3)},
                      "note": "all-gather leaves [rank][M][N/ranks] slabs that still need a re-layout pass; the fused "
                              "epilogue writes row-major M x N directly; peer bytes per GPU %.0f MB" %
                              ((world - 1) * M * nl * 2 / 1e6)}
