@@ -14,11 +14,17 @@
 //           1, 2 "mn_small": every tile is cut into `splits` K ranges and the partial sums are
 //                 added in split order 0..S-1, so the result does not depend on timing (replaces
 //                 k_large_kernel, mn_small.hip:10-137, which instead shrinks the tile to get more
-//                 blocks).  MODE 2 (S <= 8): the S CTAs of a tile form a thread-block cluster, each
-//                 leaves its fp32 partial tile in its own shared memory, and after a cluster barrier
-//                 every CTA reduces 128/S rows straight out of its peers' shared memory (DSMEM):
-//                 no workspace, no atomics.  MODE 1 (any S, also pair tiles): partial sums go to an
-//                 fp32 workspace and whoever finishes a tile last adds them.
+//                 blocks).  MODE 2 (S <= 8; the host uses it up to 6): the S CTAs of a tile form a
+//                 thread-block cluster, each leaves its fp32 partial tile in its own shared memory,
+//                 and after a cluster barrier every CTA reduces 128/S rows straight out of its
+//                 peers' shared memory (DSMEM): no workspace, no atomics.  MODE 1 (any S, also pair
+//                 tiles): partial sums go to an fp32 workspace and whoever finishes a tile last adds
+//                 them.
+//           3 stream-K: the K blocks of all tiles are dealt out evenly over the CTAs; a tile that
+//                 falls to several CTAs is finished by the one that holds its first K block, from
+//                 partial tiles the others leave in the workspace (added in K order).
+// The epilogue stores a finished tile to one or several destinations (CMaps): the caller's C, and
+// for the fused distribution of an N-sharded GEMM the peer-mapped C of the other GPUs.
 //
 // Warp roles (no __syncthreads in the main loop; registers are moved from the first warpgroup
 // to the promotion warps with setmaxnreg: 168 at launch, then 64 for warps 0-3 and 216 for the
@@ -30,8 +36,8 @@
 //              byte-wise transposing copy of the reference (mn_large.hip:40-48) has no
 //              counterpart here.
 //   warp 1     MMA issuer.  Per 128-K block: four tcgen05.mma kind::f8f6f4 (K = 32 each) into a
-//              fresh TMEM buffer (the first one overwrites), then commits that free the
-//              shared-memory stage and publish the TMEM buffer.
+//              fresh TMEM buffer (the first one overwrites), then commits that publish the TMEM
+//              buffer and free the shared-memory stage.
 //   warp 2     TMA producer for a_scale: boxes of 128 rows x 8 K blocks into a small ring, so the
 //              promotion warps never wait on a global load (mn_large.hip:50-55 stages the
 //              pre-multiplied scales in LDS for the same reason) and pay one barrier round trip
@@ -40,7 +46,8 @@
 //   warps 4..  promotion + epilogue.  TMEM lane = C row, so a thread owns one row and 128
 //              columns; per K block it reads the partial sums with tcgen05.ld, 64 columns at a
 //              time, and does
-//              acc = fma(a_scale*b_scale, partial, acc) two columns at a time (mn_large.hip:99-106).
+//              acc = fma(a_scale*b_scale, partial, acc) two columns at a time (mn_large.hip:99-106);
+//              the TMEM buffer goes back to the MMA warp as soon as its last columns are in registers.
 //              The running sums stay in registers, so the MMA warp is already filling TMEM for
 //              the next tile while these warps convert to bf16, stage through swizzled shared
 //              memory and hand C to TMA stores.
