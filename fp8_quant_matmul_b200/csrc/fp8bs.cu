@@ -579,12 +579,16 @@ static float host_e4m3fn_to_float(uint8_t b)
     return (b & 0x80) ? -v : v;
 }
 
+constexpr int HOST_CHUNKS = 4;   // column chunks fp8bs_gemm_host pipelines (copy in, GEMM, copy out)
+
 struct fp8bs_host_ctx_impl {
     size_t max_M, max_N, max_K;
     void *dA, *dB, *dAs, *dBs, *dC, *dW;
     void *hA, *hB, *hAs, *hBs, *hC;
     size_t w_bytes;
-    cudaStream_t stream;
+    cudaStream_t stream;                 // GEMM launches
+    cudaStream_t s_in, s_out;            // host-to-device and device-to-host copies: one DMA engine each way
+    cudaEvent_t e_a, e_b[HOST_CHUNKS], e_g[HOST_CHUNKS];
 };
 
 }  // namespace fp8bs
@@ -853,7 +857,13 @@ int fp8bs_host_ctx_create(fp8bs_host_ctx** out, size_t max_M, size_t max_N, size
               cudaMallocHost(&c->hAs, max_M * KB * 4) == cudaSuccess && cudaMallocHost(&c->hBs, BSCALE_MAX_BYTES) == cudaSuccess &&
               cudaMallocHost(&c->hC, max_M * max_N * 2) == cudaSuccess &&
               cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) == cudaSuccess &&
+              cudaStreamCreateWithFlags(&c->s_in, cudaStreamNonBlocking) == cudaSuccess &&
+              cudaStreamCreateWithFlags(&c->s_out, cudaStreamNonBlocking) == cudaSuccess &&
+              cudaEventCreateWithFlags(&c->e_a, cudaEventDisableTiming) == cudaSuccess &&
               cudaMemset(c->dW, 0, COUNTER_BYTES) == cudaSuccess;
+    for (int j = 0; ok && j < HOST_CHUNKS; ++j)
+        ok = cudaEventCreateWithFlags(&c->e_b[j], cudaEventDisableTiming) == cudaSuccess &&
+             cudaEventCreateWithFlags(&c->e_g[j], cudaEventDisableTiming) == cudaSuccess;
     if (!ok) {
         tl_last_cuda_error = static_cast<int>(cudaGetLastError());
         fp8bs_host_ctx_destroy(reinterpret_cast<fp8bs_host_ctx*>(c));
@@ -868,6 +878,13 @@ int fp8bs_host_ctx_destroy(fp8bs_host_ctx* ctx)
     if (!ctx) return FP8BS_OK;
     fp8bs_host_ctx_impl* c = reinterpret_cast<fp8bs_host_ctx_impl*>(ctx);
     if (c->stream) cudaStreamDestroy(c->stream);
+    if (c->s_in) cudaStreamDestroy(c->s_in);
+    if (c->s_out) cudaStreamDestroy(c->s_out);
+    if (c->e_a) cudaEventDestroy(c->e_a);
+    for (int j = 0; j < HOST_CHUNKS; ++j) {
+        if (c->e_b[j]) cudaEventDestroy(c->e_b[j]);
+        if (c->e_g[j]) cudaEventDestroy(c->e_g[j]);
+    }
     cudaFree(c->dA); cudaFree(c->dB); cudaFree(c->dAs); cudaFree(c->dBs); cudaFree(c->dC); cudaFree(c->dW);
     cudaFreeHost(c->hA); cudaFreeHost(c->hB); cudaFreeHost(c->hAs); cudaFreeHost(c->hBs); cudaFreeHost(c->hC);
     (void)cudaGetLastError();
@@ -900,15 +917,46 @@ int fp8bs_gemm_host(fp8bs_host_ctx* ctx, uint16_t* C, const void* A, const void*
         return FP8BS_ERR_SHAPE;
     const size_t KB = K / 128, sn = (static_cast<size_t>(n_total) + 127) / 128;
     if (sn * KB * 4 > BSCALE_MAX_BYTES) return FP8BS_ERR_SHAPE;
-    CUDA_TRY(cudaMemcpyAsync(c->dA, A, static_cast<size_t>(M) * K, cudaMemcpyHostToDevice, c->stream));
-    CUDA_TRY(cudaMemcpyAsync(c->dB, B, static_cast<size_t>(N) * K, cudaMemcpyHostToDevice, c->stream));
-    CUDA_TRY(cudaMemcpyAsync(c->dAs, a_scale, static_cast<size_t>(M) * KB * 4, cudaMemcpyHostToDevice, c->stream));
-    CUDA_TRY(cudaMemcpyAsync(c->dBs, b_scale, sn * KB * 4, cudaMemcpyHostToDevice, c->stream));
-    rc = gemm_impl(c->dA, c->dB, static_cast<const float*>(c->dAs), static_cast<const float*>(c->dBs), c->dC, M, N, K,
-                   n0, n_total, FP8BS_PATH_AUTO, 0, 0, c->dW, c->w_bytes, c->stream);
-    if (rc) return rc;
-    CUDA_TRY(cudaMemcpyAsync(C, c->dC, static_cast<size_t>(M) * N * 2, cudaMemcpyDeviceToHost, c->stream));
+    // Pipeline over column chunks: while chunk j is multiplied, the columns of B for chunk j + 1 come in on one copy
+    // engine and the columns of C of chunk j - 1 go out on the other.  A chunk is a run of whole 128-column blocks;
+    // on the device its B columns ([K][Nc], contiguous) and its C ([M][Nc]) sit at the chunk's offset in dB / dC.
+    const int nblk = (N + 127) / 128;
+    int chunks = (static_cast<size_t>(N) * K + static_cast<size_t>(M) * N * 2 >= (static_cast<size_t>(4) << 20)) ? HOST_CHUNKS : 1;
+    if (chunks > nblk / 4) chunks = nblk / 4 > 0 ? nblk / 4 : 1;      // at least 512 columns per chunk
+    const uint8_t* hB = static_cast<const uint8_t*>(B);
+    CUDA_TRY(cudaMemcpyAsync(c->dA, A, static_cast<size_t>(M) * K, cudaMemcpyHostToDevice, c->s_in));
+    CUDA_TRY(cudaMemcpyAsync(c->dAs, a_scale, static_cast<size_t>(M) * KB * 4, cudaMemcpyHostToDevice, c->s_in));
+    CUDA_TRY(cudaMemcpyAsync(c->dBs, b_scale, sn * KB * 4, cudaMemcpyHostToDevice, c->s_in));
+    CUDA_TRY(cudaEventRecord(c->e_a, c->s_in));
+    CUDA_TRY(cudaStreamWaitEvent(c->stream, c->e_a, 0));
+    for (int j = 0; j < chunks; ++j) {
+        const int c0 = (nblk * j / chunks) * 128;
+        int c1 = (nblk * (j + 1) / chunks) * 128;
+        if (c1 > N) c1 = N;
+        const int nc = c1 - c0;
+        uint8_t* dBj = static_cast<uint8_t*>(c->dB) + static_cast<size_t>(c0) * K;
+        __nv_bfloat16* dCj = static_cast<__nv_bfloat16*>(c->dC) + static_cast<size_t>(c0) * M;
+        if (chunks == 1) CUDA_TRY(cudaMemcpyAsync(dBj, hB, static_cast<size_t>(N) * K, cudaMemcpyHostToDevice, c->s_in));
+        else CUDA_TRY(cudaMemcpy2DAsync(dBj, nc, hB + c0, N, nc, K, cudaMemcpyHostToDevice, c->s_in));
+        CUDA_TRY(cudaEventRecord(c->e_b[j], c->s_in));
+        CUDA_TRY(cudaStreamWaitEvent(c->stream, c->e_b[j], 0));
+        rc = gemm_impl(c->dA, dBj, static_cast<const float*>(c->dAs), static_cast<const float*>(c->dBs), dCj, M, nc, K,
+                       n0 + c0, n_total, FP8BS_PATH_AUTO, 0, 0, c->dW, c->w_bytes, c->stream);
+        if (rc) {
+            (void)cudaStreamSynchronize(c->s_in);
+            (void)cudaStreamSynchronize(c->stream);
+            (void)cudaStreamSynchronize(c->s_out);
+            return rc;
+        }
+        CUDA_TRY(cudaEventRecord(c->e_g[j], c->stream));
+        CUDA_TRY(cudaStreamWaitEvent(c->s_out, c->e_g[j], 0));
+        if (chunks == 1) CUDA_TRY(cudaMemcpyAsync(C, dCj, static_cast<size_t>(M) * N * 2, cudaMemcpyDeviceToHost, c->s_out));
+        else CUDA_TRY(cudaMemcpy2DAsync(C + c0, static_cast<size_t>(N) * 2, dCj, static_cast<size_t>(nc) * 2,
+                                        static_cast<size_t>(nc) * 2, M, cudaMemcpyDeviceToHost, c->s_out));
+    }
+    CUDA_TRY(cudaStreamSynchronize(c->s_out));
     CUDA_TRY(cudaStreamSynchronize(c->stream));
+    CUDA_TRY(cudaStreamSynchronize(c->s_in));
     return FP8BS_OK;
 }
 
