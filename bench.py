@@ -244,7 +244,8 @@ def run_gpu_arm(args, rank, world):
     dist = None
     if world > 1:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=300))
 
     def barrier():
         if dist is not None:
@@ -410,7 +411,14 @@ def run_gpu_arm(args, rank, world):
             dB = torch.from_numpy(f.gen_normal_e4m3(nl * K, 9002 + rank)).to(dev)
             dAs = torch.from_numpy(f.gen_uniform_f32(M * (K // 128), 9003, 0.01, 1.0)).to(dev)
             dBs = torch.from_numpy(f.gen_uniform_f32(((N + 127) // 128) * (K // 128), 9004, 0.01, 1.0)).to(dev)
-            c_full = symm.empty((M, N), dtype=torch.bfloat16, device=dev)
+            c_full = None
+            try:
+                c_full = symm.empty((M, N), dtype=torch.bfloat16, device=dev)
+            except Exception:
+                pass
+            # every rank takes the same branch: the rendezvous and the timed loops below are collective
+            if max_over_ranks([0.0 if c_full is not None else 1.0])[0] > 0.0:
+                raise RuntimeError("symmetric memory could not be allocated on every rank")
             hdl = symm.rendezvous(c_full, dist.group.WORLD.group_name)
             ptrs = [int(x) for x in hdl.buffer_ptrs]
             c_own = torch.empty((M, nl), dtype=torch.bfloat16, device=dev)
