@@ -170,3 +170,21 @@ def test_fnuz_to_fn_preserves_values():
         with pytest.raises(f.Fp8bsError) as e:
             f.fnuz_to_fn(np.array([0x40, bb], dtype=np.uint8))
         assert e.value.code == -9 and e.value.bad_index == 1
+
+
+def test_stream_k_is_never_chosen_above_one_wave_of_tiles():
+    # measured: with more tiles than SMs the stream-K schedule loses its L2 sharing and runs up to 2x slower than the
+    # tile-per-CTA kernel, so the dispatcher offers it only on request there
+    from fp8_quant_matmul_b200.shard import plan_n_shards
+    for M in (1024, 6144, 16384):
+        for (N, K) in ((1536, 7168), (3072, 1536), (576, 7168), (7168, 256), (7168, 2048), (4608, 7168), (7168, 2304),
+                       (512, 7168), (4096, 512)):
+            for g in (1, 2, 4, 8):
+                for (_, nl) in set(plan_n_shards(N, g)):
+                    path, splits, tile_n = f.select_path(M, nl, K)
+                    if tile_n & f.STREAM_K:
+                        assert (M // 128) * -(-nl // (tile_n & 0xFFF)) <= 148
+                    # the library only ever asks for a workspace it would use
+                    assert (f.workspace_bytes(M, nl, K) > 0) == bool(tile_n & (f.SPLIT_WORKSPACE | f.STREAM_K))
+    # forcing it is always possible, and it then reports its workspace
+    assert f.workspace_bytes(16384, 1536, 7168, f.PATH_MN_SMALL, 1, 256 | f.STREAM_K) == 65536 + 148 * 256 * 128 * 4
