@@ -930,6 +930,47 @@ int fp8bs_gemm_host(fp8bs_host_ctx* ctx, uint16_t* C, const void* A, const void*
     int chunks = (static_cast<size_t>(N) * K + static_cast<size_t>(M) * N * 2 >= (static_cast<size_t>(4) << 20)) ? HOST_CHUNKS : 1;
     if (chunks > nblk / 4) chunks = nblk / 4 > 0 ? nblk / 4 : 1;      // at least 512 columns per chunk
     const uint8_t* hB = static_cast<const uint8_t*>(B);
+    const size_t a_bytes = static_cast<size_t>(M) * K, b_bytes = static_cast<size_t>(N) * K, c_bytes = static_cast<size_t>(M) * N * 2;
+    if (a_bytes > b_bytes + c_bytes && a_bytes >= (static_cast<size_t>(8) << 20) && M >= 4 * 256) {
+        // A is the bulk of the traffic: pipeline over row chunks instead.  B and b_scale go in first; then, chunk by
+        // chunk, the rows of A and a_scale (as [K][Mc] and [K/128][Mc], contiguous on the device), the GEMM on those
+        // rows, and the copy-out of the finished rows of C, which are contiguous in the caller's buffer.
+        const uint8_t* hA = static_cast<const uint8_t*>(A);
+        const int mblk = (M + 127) / 128;
+        const int mchunks = mblk / 2 < HOST_CHUNKS ? (mblk / 2 > 0 ? mblk / 2 : 1) : HOST_CHUNKS;
+        CUDA_TRY(cudaMemcpyAsync(c->dB, hB, b_bytes, cudaMemcpyHostToDevice, c->s_in));
+        CUDA_TRY(cudaMemcpyAsync(c->dBs, b_scale, sn * KB * 4, cudaMemcpyHostToDevice, c->s_in));
+        for (int j = 0; j < mchunks; ++j) {
+            const int r0 = (mblk * j / mchunks) * 128;
+            int r1 = (mblk * (j + 1) / mchunks) * 128;
+            if (r1 > M) r1 = M;
+            const int mc = r1 - r0;
+            uint8_t* dAj = static_cast<uint8_t*>(c->dA) + static_cast<size_t>(r0) * K;
+            float* dAsj = static_cast<float*>(c->dAs) + static_cast<size_t>(r0) * KB;
+            __nv_bfloat16* dCj = static_cast<__nv_bfloat16*>(c->dC) + static_cast<size_t>(r0) * N;
+            CUDA_TRY(cudaMemcpy2DAsync(dAj, mc, hA + r0, M, mc, K, cudaMemcpyHostToDevice, c->s_in));
+            CUDA_TRY(cudaMemcpy2DAsync(dAsj, static_cast<size_t>(mc) * 4, a_scale + r0, static_cast<size_t>(M) * 4,
+                                       static_cast<size_t>(mc) * 4, KB, cudaMemcpyHostToDevice, c->s_in));
+            CUDA_TRY(cudaEventRecord(c->e_b[j], c->s_in));
+            CUDA_TRY(cudaStreamWaitEvent(c->stream, c->e_b[j], 0));
+            rc = gemm_impl(dAj, c->dB, dAsj, static_cast<const float*>(c->dBs), dCj, mc, N, K, n0, n_total,
+                           FP8BS_PATH_AUTO, 0, 0, c->dW, c->w_bytes, c->stream);
+            if (rc) {
+                (void)cudaStreamSynchronize(c->s_in);
+                (void)cudaStreamSynchronize(c->stream);
+                (void)cudaStreamSynchronize(c->s_out);
+                return rc;
+            }
+            CUDA_TRY(cudaEventRecord(c->e_g[j], c->stream));
+            CUDA_TRY(cudaStreamWaitEvent(c->s_out, c->e_g[j], 0));
+            CUDA_TRY(cudaMemcpyAsync(C + static_cast<size_t>(r0) * N, dCj, static_cast<size_t>(mc) * N * 2,
+                                     cudaMemcpyDeviceToHost, c->s_out));
+        }
+        CUDA_TRY(cudaStreamSynchronize(c->s_out));
+        CUDA_TRY(cudaStreamSynchronize(c->stream));
+        CUDA_TRY(cudaStreamSynchronize(c->s_in));
+        return FP8BS_OK;
+    }
     CUDA_TRY(cudaMemcpyAsync(c->dA, A, static_cast<size_t>(M) * K, cudaMemcpyHostToDevice, c->s_in));
     CUDA_TRY(cudaMemcpyAsync(c->dAs, a_scale, static_cast<size_t>(M) * KB * 4, cudaMemcpyHostToDevice, c->s_in));
     CUDA_TRY(cudaMemcpyAsync(c->dBs, b_scale, sn * KB * 4, cudaMemcpyHostToDevice, c->s_in));

@@ -328,6 +328,30 @@ def test_host_context_end_to_end():
         ctx.close()
 
 
+@pytest.mark.parametrize("shape,n0,n_total", [((512, 4096, 1024), 0, 4096), ((2048, 256, 4096), 0, 256),
+                                              ((2048, 192, 4096), 64, 320), ((2064, 272, 4096), 0, 272)],
+                         ids=["column-chunks", "row-chunks", "row-chunks-of-a-shard", "row-chunks-ragged"])
+def test_host_context_pipelined_paths(shape, n0, n_total):
+    # large enough for the host call to pipeline copy-in, GEMM and copy-out over column or row chunks
+    M, N, K = shape
+    ctx = f.HostContext(M, N, K)
+    try:
+        A, Bfull, a_s, b_s = h.make_inputs(M, n_total, K, seed=57)
+        B = np.ascontiguousarray(Bfull.reshape(K, n_total)[:, n0:n0 + N]).ravel()
+        hA = ctx.buffer(0, M * K, np.uint8); hA[:] = A
+        hB = ctx.buffer(1, N * K, np.uint8); hB[:] = B
+        hAs = ctx.buffer(2, a_s.nbytes, np.float32); hAs[:] = a_s
+        hBs = ctx.buffer(3, b_s.nbytes, np.float32); hBs[:] = b_s
+        hC = ctx.buffer(4, M * N * 2, np.uint16)
+        ref = h.oracle_gemm(A, Bfull, a_s, b_s, M, n_total, K)[:, n0:n0 + N]
+        for _ in range(2):
+            hC[:] = 0x7FC0
+            ctx.gemm(hC, hA, hB, hAs, hBs, M, N, K, n0, n_total)
+            assert_parity(np.ascontiguousarray(ref), hC.reshape(M, N))
+    finally:
+        ctx.close()
+
+
 def test_bounded_wait_reports_a_timeout_and_leaves_the_context_usable():
     # failure detection without a GPU fault: a wait on a barrier nothing sets runs out, the kernel returns a status
     lib = f.lib()
