@@ -10,15 +10,22 @@ the GEMM path), and a shape's time is the max over ranks.  Rank 0 prints ONE JSO
 
   value      geomean over the 18 shapes of the mean kernel latency in microseconds, operands resident
              in HBM, measured with CUDA events around CUDA-graph replays that rotate over enough
-             distinct buffer sets to exceed twice the L2 (so every launch reads its operands from HBM)
+             distinct buffer sets to exceed twice the L2 (so every launch reads its operands from HBM);
+             `shapes` also gives the min and median over the replays and `isolated_us`, one launch
+             between two events with nothing queued behind it (the reference's loop, sgemm.cu:96-126)
   e2e        the same geomean through the host-buffer entry point fp8bs_gemm_host: H2D of A, B and
              both scale arrays from pinned memory, the GEMM, D2H of C, inside the timed region
-  roofline   the dominant kernel (the full-K kernel the dispatcher picks for M=6144 N=4608 K=7168) against the tensor peak
+  roofline   the dominant kernel (the full-K kernel the dispatcher picks for M=6144 N=4608 K=7168)
+             against the tensor peak, per GPU; roofline_hbm: the output-bound and the small shapes
+             against the measured copy bandwidth, per GPU
+  parity     how many rows of how many shards this run compared with the CPU checker before timing
   cpu_baseline  the reference's CPU path (dequantise -> gemmCPU of utils.h:65-76 -> bf16) when
-             oracle/_ref is present, else the CPU restatement in oracle/, on a bounded row sample
+             oracle/_ref is present, else the CPU restatement in oracle/: BASELINE config 0 whole,
+             the other shapes on a bounded row sample
   m16384     aggregate TFLOP/s on the M=16384 variants of the nine (N, K) pairs, same partition
 
---impl reference times only that CPU path (rank 0; other ranks exit) and prints the same line shape.
+--impl reference times only that CPU path (rank 0; other ranks exit) and prints the same line shape;
+it loads nothing of this repository except the checker libraries under oracle/.
 """
 import argparse
 import json
@@ -38,9 +45,13 @@ L2_BYTES = 126 * 1024 * 1024
 NK_PAIRS = [(1536, 7168), (3072, 1536), (576, 7168), (7168, 256), (7168, 2048), (4608, 7168), (7168, 2304),
             (512, 7168), (4096, 512)]
 SHAPES_18 = [(m, n, k) for m in (1024, 6144) for (n, k) in NK_PAIRS]
-DOMINANT = (6144, 4608, 7168)
+CONFIG0 = (1024, 1536, 7168)            # the reference's CPU-runnable case
+DOMINANT = (6144, 4608, 7168)           # compute-bound: tensor roofline
+HBM_SHAPES = [(6144, 7168, 256), (6144, 4096, 512), (1024, 512, 7168)]   # output-bound / small: HBM roofline
 NOMINAL_FP8_TFLOPS = 4500.0
 NOMINAL_HBM_GBS = 8000.0
+PARITY_ROWS = 16                        # rows of every shard compared with the CPU checker before timing
+FUSED_PARITY_ROWS = 64                  # rows of the peer-written C compared after the fused-distribution leg
 
 
 def algorithmic_bytes(M, N, K, n_total=None):
@@ -123,56 +134,104 @@ class ClockSampler:
 
 
 # ----------------------------------------------------------------------------- CPU arm -------
+# Inputs of the CPU arm are made and decoded with numpy alone, so that this arm loads none of the GPU library.
+def np_e4m3fn_table():
+    b = np.arange(256)
+    e, m = (b >> 3) & 15, b & 7
+    v = np.where(e == 0, m * 2.0 ** -9, (8 + m) * 2.0 ** (e - 10.0)).astype(np.float32)
+    v[(e == 15) & (m == 7)] = np.nan
+    return np.where(b & 0x80, -v, v).astype(np.float32)
+
+
+def np_gen_normal_e4m3(n, seed):
+    """n e4m3fn bytes with the benchmark's element distribution: N(0,1) rounded to nearest even,
+    |x| <= 240, |x| < 2^-6 -> +0 (so every value is a normal number of the format)."""
+    x = np.random.default_rng(seed).standard_normal(n, dtype=np.float32)
+    u = np.clip(x, -240.0, 240.0).view(np.uint32).astype(np.uint64)
+    u = (u + 0x7FFFF + ((u >> 20) & 1)) & ~np.uint64(0xFFFFF)          # keep 3 mantissa bits, ties to even
+    sign = ((u >> 24) & 0x80).astype(np.uint8)
+    exp = ((u >> 23) & 0xFF).astype(np.int32) - 127 + 7                # e4m3fn bias 7
+    mant = ((u >> 20) & 7).astype(np.uint8)
+    out = sign | (np.clip(exp, 0, 15).astype(np.uint8) << 3) | mant
+    out[exp < 1] = 0                                                   # below 2^-6: +0
+    return out
+
+
+def np_gen_uniform(n, seed, lo, hi):
+    return np.random.default_rng(seed).uniform(lo, hi, n).astype(np.float32)
+
+
 def _cpu_libs():
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import helpers as h
     return h, h.ref_lib()
 
 
-def cpu_path_seconds(h, ref, f, M, N, K, rows, threads):
-    """Estimated seconds for the CPU path on the full M x N x K problem, from a `rows`-row sample.
-    With oracle/_ref: the reference's own code (dequantise fp32 -> gemmCPU, utils.h:65-76 -> bf16),
-    run on all host threads over row slabs.  Otherwise the CPU restatement in oracle/ (OpenMP)."""
+def cpu_path_time(h, ref, table, M, N, K, rows, threads):
+    """Seconds of the CPU path on `rows` rows of an M x N x K problem (rows = M: the whole problem), split into
+    the part paid once per problem (dequantising B) and the part that grows with the rows.
+    With oracle/_ref: the reference's own code (dequantise fp32 -> gemmCPU, utils.h:65-76 -> bf16), run on all host
+    threads over row slabs.  Otherwise the CPU restatement in oracle/ (OpenMP)."""
     rows = min(rows, M)
-    A, B, a_s, b_s = h.make_inputs(rows, N, K, seed=1)       # a rows x K problem stands for rows of the full one
+    sn = (N + 127) // 128
+    A = np_gen_normal_e4m3(rows * K, 1)                      # rows x K column-major stands for rows of the full A
+    B = np_gen_normal_e4m3(N * K, 2)
+    a_s = np_gen_uniform(rows * (K // 128), 3, 0.01, 1.0)
+    b_s = np_gen_uniform(sn * (K // 128), 4, 0.01, 1.0)
     if ref is None:
         t0 = time.perf_counter()
         h.oracle_gemm(A, B, a_s, b_s, rows, N, K)
-        return (time.perf_counter() - t0) * (M / rows)
-    sn = (N + 127) // 128
+        return 0.0, time.perf_counter() - t0
     t0 = time.perf_counter()
-    Bd = np.ascontiguousarray(f.e4m3fn_to_float(B).reshape(K, N) *
+    Bd = np.ascontiguousarray(table[B].reshape(K, N) *
                               np.repeat(np.repeat(b_s.reshape(K // 128, sn), 128, axis=0), 128, axis=1)[:, :N],
                               dtype=np.float32)
     t_b = time.perf_counter() - t0
     t0 = time.perf_counter()
-    Ad = np.ascontiguousarray(f.e4m3fn_to_float(A).reshape(K, rows).T *
-                              np.repeat(a_s.reshape(K // 128, rows).T, 128, axis=1), dtype=np.float32)
+    Ad = np.ascontiguousarray(table[A].reshape(K, rows).T * np.repeat(a_s.reshape(K // 128, rows).T, 128, axis=1),
+                              dtype=np.float32)
     Cf = np.empty((rows, N), np.float32)
     ref.ref_gemmCPU_mt(Cf.ctypes.data, Ad.ctypes.data, Bd.ctypes.data, rows, N, K, threads)
     h.f32_to_bf16_bits(Cf)
-    t_rows = time.perf_counter() - t0
-    return t_b + t_rows * (M / rows)
+    return t_b, time.perf_counter() - t0
 
 
-def cpu_sweep(rows_per_shape, shapes=SHAPES_18):
-    import fp8_quant_matmul_b200 as f
+def cpu_sweep(rows_per_shape, shapes=SHAPES_18, full_shapes=(CONFIG0,), scaling_check=True):
+    """The CPU path over the benchmark's shapes: `full_shapes` are run whole, the rest on a row sample whose time is
+    scaled by M / rows; two sample sizes on one shape show that the time is proportional to the rows."""
     h, ref = _cpu_libs()
+    table = np_e4m3fn_table()
     threads = os.cpu_count() or 1
     if ref is None:
         threads = h.oracle_lib().oracle_num_threads()
     else:
         threads = min(threads, 64)
         rows_per_shape = max(rows_per_shape, threads)      # at least one row per host thread
-    us = []
+    us, how = [], []
     for (M, N, K) in shapes:
-        us.append(cpu_path_seconds(h, ref, f, M, N, K, rows_per_shape, threads) * 1e6)
-    return {"value": geomean(us), "unit": "us", "cores": threads, "kind": "reference" if ref is not None else "port",
-            "sample": "%d rows of each of the %d shapes (all N, all K), time scaled by M/rows; %s" %
-                      (rows_per_shape, len(shapes),
-                       "dequantise -> reference gemmCPU (utils.h:65-76) on row slabs over all host threads -> bf16"
-                       if ref is not None else "CPU restatement of ref_kernel (oracle/), OpenMP"),
-            "per_shape_us": [round(u, 1) for u in us]}
+        if (M, N, K) in full_shapes:
+            t_b, t_rows = cpu_path_time(h, ref, table, M, N, K, M, threads)
+            us.append((t_b + t_rows) * 1e6)
+            how.append("full")
+        else:
+            t_b, t_rows = cpu_path_time(h, ref, table, M, N, K, rows_per_shape, threads)
+            us.append((t_b + t_rows * (M / min(rows_per_shape, M))) * 1e6)
+            how.append("%d rows" % min(rows_per_shape, M))
+    out = {"value": geomean(us), "unit": "us", "cores": threads, "kind": "reference" if ref is not None else "port",
+           "sample": "%s whole (\"full\"); %d rows of each other shape (all N, all K), the row part of the time scaled "
+                     "by M/rows; %s" %
+                     (", ".join("%dx%dx%d" % s for s in full_shapes if s in shapes) or "no shape", rows_per_shape,
+                      "dequantise -> reference gemmCPU (utils.h:65-76) on row slabs over all host threads -> bf16"
+                      if ref is not None else "CPU restatement of ref_kernel (oracle/), OpenMP"),
+           "per_shape_us": [round(u, 1) for u in us], "per_shape_sample": how}
+    if scaling_check:
+        M, N, K = 6144, 4096, 512
+        _, t1 = cpu_path_time(h, ref, table, M, N, K, rows_per_shape, threads)
+        _, t2 = cpu_path_time(h, ref, table, M, N, K, 2 * rows_per_shape, threads)
+        out["row_scaling_check"] = {"shape": [M, N, K], "rows": [rows_per_shape, 2 * rows_per_shape],
+                                    "seconds": [round(t1, 4), round(t2, 4)], "ratio": round(t2 / t1, 3),
+                                    "expected_ratio": 2.0}
+    return out
 
 
 def run_reference_arm(args, rank):
@@ -180,16 +239,19 @@ def run_reference_arm(args, rank):
         return
     rows = 16
     for _ in range(args.warmup):
-        cpu_sweep(2, SHAPES_18[:2])
+        cpu_sweep(2, SHAPES_18[1:3], full_shapes=(), scaling_check=False)
     t0 = time.perf_counter()
-    vals = [cpu_sweep(rows) for _ in range(args.steps)]
+    vals = [cpu_sweep(rows, scaling_check=(s == 0)) for s in range(args.steps)]
     wall = time.perf_counter() - t0
     best = min(vals, key=lambda v: v["value"])
+    if "row_scaling_check" not in best:
+        best["row_scaling_check"] = vals[0]["row_scaling_check"]
     line = {"metric": "geomean_latency_us_18_shapes", "value": best["value"], "unit": "us", "impl": "reference",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": wall * 1e3 / args.steps,
             "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
             "dtype": "fp8_e4m3 operands, fp32 accumulate, bf16 out", "data": "synthetic",
-            "config": {"workload": "18-shape sweep M in {1024,6144} x 9 (N,K) pairs, CPU path on a row sample"},
+            "config": {"workload": "18-shape sweep M in {1024,6144} x 9 (N,K) pairs, CPU path; 1024x1536x7168 whole, "
+                                   "the others on a row sample"},
             "cpu_baseline": best,
             "e2e": {"value": best["value"], "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     emit(line)
@@ -217,10 +279,13 @@ class ShapeBench:
         self.graph = None
         self.launches_per_replay = nsets
 
+    def launch(self, s):
+        A, B, a_s, b_s, C = self.sets[s]
+        self.f.gemm(A, B, a_s, b_s, C, self.M, self.nl, self.K, n0=self.n0, n_total=self.N, workspace=self.workspace)
+
     def launch_all_sets(self):
-        f = self.f
-        for (A, B, a_s, b_s, C) in self.sets:
-            f.gemm(A, B, a_s, b_s, C, self.M, self.nl, self.K, n0=self.n0, n_total=self.N, workspace=self.workspace)
+        for s in range(len(self.sets)):
+            self.launch(s)
 
     def capture(self):
         torch = self.torch
@@ -230,6 +295,97 @@ class ShapeBench:
         with torch.cuda.graph(self.graph):
             self.launch_all_sets()
         torch.cuda.synchronize()
+
+    def check(self, h, nrows, which_set=-1):
+        """Compare `nrows` evenly spaced rows of one buffer set's C (as the launches above left it) with the CPU
+        checker; raises on any element outside the tolerance.  Returns the number of rows compared."""
+        torch = self.torch
+        A, B, a_s, b_s, C = self.sets[which_set]
+        rows = np.unique(np.linspace(0, self.M - 1, nrows).astype(np.int32))
+        ref = h.oracle_gemm(A.cpu().numpy(), B.cpu().numpy(), a_s.cpu().numpy(), b_s.cpu().numpy(), self.M, self.nl,
+                            self.K, n0=self.n0, n_total=self.N, rows=rows)
+        bad, first, maxerr = h.mismatches(ref, C.view(torch.int16).cpu().numpy().view(np.uint16)[rows])
+        if bad:
+            raise AssertionError("bench: M=%d N=%d (columns %d..%d) K=%d disagrees with the CPU checker: %d mismatches, "
+                                 "first at %d, max err %g" % (self.M, self.N, self.n0, self.n0 + self.nl, self.K, bad,
+                                                              first, maxerr))
+        return len(rows)
+
+    def isolated_us(self, reps=9):
+        """One launch between two events, nothing queued behind it (the reference's loop, sgemm.cu:96-126):
+        median over `reps` launches after one that is dropped."""
+        torch = self.torch
+        out = []
+        for i in range(reps + 1):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            self.launch(i % len(self.sets))
+            e1.record()
+            e1.synchronize()
+            if i:
+                out.append(e0.elapsed_time(e1) * 1e3)
+        return float(np.median(out))
+
+
+def time_device_kernel(torch, fn, reps=20, warm=3):
+    """Mean microseconds of fn() (one kernel on the current stream) over `reps` back-to-back calls."""
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / reps
+
+
+def format_kernels_bench(torch, f, dev, hbm_gbs):
+    """Throughput of the kernels either side of the GEMM (quantize.py:16-67, check.cu:17-22), against the copy
+    bandwidth.  Each rotates over three input sets larger than L2 in total."""
+    out = {}
+    M, N, K = 6144, 4608, 7168
+    xs = [torch.randn((M, K), dtype=torch.float32, device=dev) for _ in range(3)]          # 3 x 176 MB
+    qa = torch.empty(M * K, dtype=torch.uint8, device=dev)
+    sa = torch.empty(M * (K // 128), dtype=torch.float32, device=dev)
+    lib, st = f.lib(), torch.cuda.current_stream(dev).cuda_stream
+    it = [0]
+
+    def row():
+        it[0] += 1
+        rc = lib.fp8bs_quantize_rowwise(xs[it[0] % 3].data_ptr(), 0, qa.data_ptr(), sa.data_ptr(), M, K, 448.0, st)
+        assert rc == 0
+    us = time_device_kernel(torch, row)
+    by = M * K * 5 + 4 * M * (K // 128)
+    out["quantize_rowwise"] = {"shape": "%dx%d fp32 -> e4m3 + a_scale" % (M, K), "us": round(us, 2), "bytes": by,
+                               "GBps": round(by / us / 1e3, 1), "frac_of_hbm_peak": round(by / us / 1e3 / hbm_gbs, 3)}
+    ws = [x[:N] for x in xs]
+    qb = torch.empty(N * K, dtype=torch.uint8, device=dev)
+    sb = torch.empty(((N + 127) // 128) * (K // 128), dtype=torch.float32, device=dev)
+
+    def blk():
+        it[0] += 1
+        rc = lib.fp8bs_quantize_block(ws[it[0] % 3].data_ptr(), 0, qb.data_ptr(), sb.data_ptr(), N, K, 448.0, st)
+        assert rc == 0
+    us = time_device_kernel(torch, blk)
+    by = N * K * 5 + 4 * sb.numel()
+    out["quantize_block"] = {"shape": "%dx%d fp32 -> e4m3 + b_scale" % (N, K), "us": round(us, 2), "bytes": by,
+                             "GBps": round(by / us / 1e3, 1), "frac_of_hbm_peak": round(by / us / 1e3 / hbm_gbs, 3)}
+    del xs, ws
+    n = M * K                                                                            # 44 MB, as A of the big shape
+    srcs = [torch.randint(8, 0x78, (n,), dtype=torch.uint8, device=dev) for _ in range(7)]  # 7 x 44 MB > 2 x L2
+    dst = torch.empty(n, dtype=torch.uint8, device=dev)
+
+    def conv():
+        it[0] += 1
+        rc = lib.fp8bs_fnuz_to_fn_device(dst.data_ptr(), srcs[it[0] % 7].data_ptr(), n, None, st)
+        assert rc == 0
+    us = time_device_kernel(torch, conv)
+    out["fnuz_to_fn_device"] = {"shape": "%d bytes" % n, "us": round(us, 2), "bytes": 2 * n,
+                                "GBps": round(2 * n / us / 1e3, 1), "frac_of_hbm_peak": round(2 * n / us / 1e3 / hbm_gbs, 3)}
+    out["how"] = "CUDA events around 20 back-to-back launches after 3 warm-up launches; peak = measured copy bandwidth"
+    return out
 
 
 def run_gpu_arm(args, rank, world):
@@ -252,14 +408,20 @@ def run_gpu_arm(args, rank, world):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def max_over_ranks(values):
+    def reduce_over_ranks(values, op="max"):
         t = torch.tensor(values, dtype=torch.float64, device=dev)
         if dist is not None:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dist.all_reduce(t, op={"max": dist.ReduceOp.MAX, "min": dist.ReduceOp.MIN, "sum": dist.ReduceOp.SUM}[op])
         return t.cpu().tolist()
 
+    def max_over_ranks(values):
+        return reduce_over_ranks(values, "max")
+
     peaks, peak_src = measured_peaks()
+    of_what = "measured" if peak_src != "fallback" else "fallback"
     min_footprint = 2 * L2_BYTES + (8 << 20)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import helpers as h
 
     # one split-K workspace for every launch of this process (captured graphs keep pointing at it)
     ws_bytes = 1 << 20
@@ -270,25 +432,16 @@ def run_gpu_arm(args, rank, world):
         raise RuntimeError("fp8bs_workspace_init failed")
     torch.cuda.synchronize()
 
-    # ---- build per-shape benches (this rank's column shard of every shape) ----
-    benches = []
+    # ---- build per-shape benches (this rank's column shard of every shape), each checked against the CPU checker ----
+    benches, checked_rows = [], 0
     for i, (M, N, K) in enumerate(SHAPES_18):
         n0, nl = plan_n_shards(N, world)[rank]
-        benches.append(ShapeBench(torch, f, dev, M, N, K, n0, nl, 1000 + 10 * i, min_footprint, workspace))
-        benches[-1].capture()
-    f.last_device_status()
-
-    # ---- quick parity guard on this rank's shard of config 0 (sampled rows) ----
-    sys.path.insert(0, os.path.join(ROOT, "tests"))
-    import helpers as h
-    b0 = benches[0]
-    rows = np.arange(0, b0.M, 64, dtype=np.int32)
-    A, B, a_s, b_s, C = b0.sets[0]
-    ref = h.oracle_gemm(A.cpu().numpy(), B.cpu().numpy(), a_s.cpu().numpy(), b_s.cpu().numpy(), b0.M, b0.nl, b0.K,
-                        n0=b0.n0, n_total=b0.N, rows=rows)
-    bad, _, _ = h.mismatches(ref, C.view(torch.int16).cpu().numpy().view(np.uint16)[rows])
-    if bad:
-        raise AssertionError("bench: GPU result disagrees with the CPU checker (%d mismatches)" % bad)
+        b = ShapeBench(torch, f, dev, M, N, K, n0, nl, 1000 + 10 * i, min_footprint, workspace)
+        b.capture()
+        f.last_device_status()
+        checked_rows += b.check(h, PARITY_ROWS)          # the last buffer set, as the captured launches see it
+        benches.append(b)
+    parity = {"shards_checked_18": len(benches), "rows_per_shard": PARITY_ROWS}
 
     def one_step(events=None):
         for i, b in enumerate(benches):
@@ -320,11 +473,17 @@ def run_gpu_arm(args, rank, world):
     # graph replays do not go through the library's launch counter: count the kernels they contain
     gpu_launches = args.steps * sum(b.launches_per_replay for b in benches) + (f.launch_count() - launches_before)
     total_ms = max_over_ranks([t_start.elapsed_time(t_end)])[0]
-    per_shape_us = []
+    per_shape_us, per_shape_min, per_shape_med = [], [], []
     for i, b in enumerate(benches):
-        us = sum(ev[s][i][0].elapsed_time(ev[s][i][1]) for s in range(args.steps)) * 1e3 / (args.steps * b.launches_per_replay)
-        per_shape_us.append(us)
+        per = [ev[s][i][0].elapsed_time(ev[s][i][1]) * 1e3 / b.launches_per_replay for s in range(args.steps)]
+        per_shape_us.append(sum(per) / len(per))
+        per_shape_min.append(min(per))
+        per_shape_med.append(float(np.median(per)))
     per_shape_us = max_over_ranks(per_shape_us)
+    per_shape_min = max_over_ranks(per_shape_min)
+    per_shape_med = max_over_ranks(per_shape_med)
+    f.last_device_status()
+    isolated = max_over_ranks([b.isolated_us() for b in benches])
     f.last_device_status()
 
     # ---- end to end through the host-buffer entry point ----
@@ -355,6 +514,7 @@ def run_gpu_arm(args, rank, world):
     e2e_us = max_over_ranks(e2e_us)
 
     # ---- M = 16384 variants: aggregate TFLOP/s under the same column partition ----
+    shard_widths = [b.nl for b in benches]
     del benches
     torch.cuda.empty_cache()
     m16 = []
@@ -362,6 +522,8 @@ def run_gpu_arm(args, rank, world):
         n0, nl = plan_n_shards(N, world)[rank]
         b = ShapeBench(torch, f, dev, 16384, N, K, n0, nl, 5000 + 10 * i, min_footprint, workspace)
         b.capture()
+        f.last_device_status()
+        checked_rows += b.check(h, PARITY_ROWS)
         for _ in range(3):
             b.graph.replay()
         barrier()
@@ -377,6 +539,11 @@ def run_gpu_arm(args, rank, world):
         del b
         torch.cuda.empty_cache()
     f.last_device_status()
+    parity["shards_checked_m16384"] = len(NK_PAIRS)
+    parity["rows_checked_this_rank"] = checked_rows
+    parity["rows_checked_all_ranks"] = int(reduce_over_ranks([checked_rows], "sum")[0])
+    parity["how"] = ("every rank compares evenly spaced rows (all columns of its shard) of each of the 18 + 9 shards with "
+                     "the CPU restatement of ref_kernel on the same inputs, |d| <= 1e-3 + 2e-2 |ref|, and raises on a mismatch")
     agg_flops = sum(2.0 * 16384 * N * K for (N, K) in NK_PAIRS)
     agg_us = sum(x["us"] for x in m16)
 
@@ -399,98 +566,74 @@ def run_gpu_arm(args, rank, world):
         us = max_over_ranks([e0.elapsed_time(e1) * 1e3 / 10])[0]
         allgather = {"shape": "C 16384 x 7168 bf16 in %d column slabs" % world, "us": round(us, 1),
                      "bus_GBps": round(out.numel() * 2 * (world - 1) / world / us / 1e3, 1)}
+        del mine, out
 
     # ---- distribution of C fused into the GEMM epilogue (fp8bs_gemm_scatter) against GEMM + all-gather ----
     fused = None
     if dist is not None:
-        try:
-            import torch.distributed._symmetric_memory as symm
-            M, N, K = 16384, 7168, 2304
-            n0, nl = plan_n_shards(N, world)[rank]
-            dA = torch.from_numpy(f.gen_normal_e4m3(M * K, 9001)).to(dev)
-            dB = torch.from_numpy(f.gen_normal_e4m3(nl * K, 9002 + rank)).to(dev)
-            dAs = torch.from_numpy(f.gen_uniform_f32(M * (K // 128), 9003, 0.01, 1.0)).to(dev)
-            dBs = torch.from_numpy(f.gen_uniform_f32(((N + 127) // 128) * (K // 128), 9004, 0.01, 1.0)).to(dev)
-            c_full = None
-            try:
-                c_full = symm.empty((M, N), dtype=torch.bfloat16, device=dev)
-            except Exception:
-                pass
-            # every rank takes the same branch: the rendezvous and the timed loops below are collective
-            if max_over_ranks([0.0 if c_full is not None else 1.0])[0] > 0.0:
-                raise RuntimeError("symmetric memory could not be allocated on every rank")
-            hdl = symm.rendezvous(c_full, dist.group.WORLD.group_name)
-            ptrs = [int(x) for x in hdl.buffer_ptrs]
-            c_own = torch.empty((M, nl), dtype=torch.bfloat16, device=dev)
-            gathered = torch.empty((world, M, nl), dtype=torch.bfloat16, device=dev)
+        fused = fused_distribution_leg(torch, f, h, dist, dev, rank, world, barrier, max_over_ranks, reduce_over_ranks,
+                                       plan_n_shards)
 
-            def timed(fn, reps=10):
-                for _ in range(3):
-                    fn()
-                barrier()
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record()
-                for _ in range(reps):
-                    fn()
-                e1.record()
-                barrier()
-                return max_over_ranks([e0.elapsed_time(e1) * 1e3 / reps])[0]
-
-            def separate():
-                f.gemm(dA, dB, dAs, dBs, c_own, M, nl, K, n0=n0, n_total=N, path=f.PATH_MN_LARGE)
-                dist.all_gather_into_tensor(gathered, c_own)
-
-            t_gemm = timed(lambda: f.gemm(dA, dB, dAs, dBs, c_own, M, nl, K, n0=n0, n_total=N, path=f.PATH_MN_LARGE))
-            t_sep = timed(separate)
-            t_fused = timed(lambda: f.gemm_scatter(dA, dB, dAs, dBs, ptrs, M, nl, K, n0, N))
-            f.last_device_status()
-            fused = {"shape": "M=16384 N=7168 K=2304, C row-major on every GPU", "gemm_only_us": round(t_gemm, 1),
-                     "gemm_then_nccl_all_gather_us": round(t_sep, 1), "gemm_with_fused_distribution_us": round(t_fused, 1),
-                     "roofline": {"bound": "slower of the GEMM alone and the peer bytes over one NVLink direction (770 GB/s measured peer copy)",
-                                  "target_us": round(max(t_gemm, (world - 1) * M * nl * 2 / 770e3), 1),
-                                  "frac": round(max(t_gemm, (world - 1) * M * nl * 2 / 770e3) / t_fused, 3)},
-                     "note": "all-gather leaves [rank][M][N/ranks] slabs that still need a re-layout pass; the fused "
-                             "epilogue writes row-major M x N directly; peer bytes per GPU %.0f MB" %
-                             ((world - 1) * M * nl * 2 / 1e6)}
-            del c_full, hdl
-        except Exception as exc:                                   # symmetric memory unavailable on this box
-            fused = {"unavailable": str(exc)[:300]}
-
+    formats = format_kernels_bench(torch, f, dev, peaks["hbm_gbs"]) if rank == 0 else None
+    torch.cuda.synchronize()
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
         return
 
-    # ---- rank 0: assemble the line ----
+    # ---- rank 0: assemble the line.  Per-GPU figures use the shard's own work; aggregates use the whole problem. ----
     shapes_out = []
-    for (M, N, K), us, e in zip(SHAPES_18, per_shape_us, e2e_us):
-        path, splits, tile_n = f.select_path(M, plan_n_shards(N, world)[0][1], K)
-        by = algorithmic_bytes(M, N, K)
-        shapes_out.append({"M": M, "N": N, "K": K, "us": round(us, 2), "tflops": round(2.0 * M * N * K / us / 1e6, 1),
-                           "GBps": round(by / us / 1e3, 1), "pct_fp8_nominal": round(2.0 * M * N * K / us / 1e6 / NOMINAL_FP8_TFLOPS * 100, 1),
-                           "pct_hbm_nominal": round(by / us / 1e3 / NOMINAL_HBM_GBS * 100, 1),
-                           "path": "mn_small" if path == f.PATH_MN_SMALL else "mn_large", "splits": splits,
-                           "tile_n": tile_n, "e2e_us": round(e, 1)})
+    for i, ((M, N, K), us, e) in enumerate(zip(SHAPES_18, per_shape_us, e2e_us)):
+        nl0 = plan_n_shards(N, world)[0][1]                       # rank 0's shard is never the narrower one
+        path, splits, tile_n = f.select_path(M, nl0, K)
+        by_gpu = algorithmic_bytes(M, nl0, K, N)
+        tf_gpu = 2.0 * M * nl0 * K / us / 1e6
+        shapes_out.append({"M": M, "N": N, "K": K, "us": round(us, 2), "min_us": round(per_shape_min[i], 2),
+                           "median_us": round(per_shape_med[i], 2), "isolated_us": round(isolated[i], 2),
+                           "tflops": round(2.0 * M * N * K / us / 1e6, 1), "tflops_per_gpu": round(tf_gpu, 1),
+                           "GBps_per_gpu": round(by_gpu / us / 1e3, 1),
+                           "pct_fp8_nominal_per_gpu": round(tf_gpu / NOMINAL_FP8_TFLOPS * 100, 1),
+                           "pct_hbm_nominal_per_gpu": round(by_gpu / us / 1e3 / NOMINAL_HBM_GBS * 100, 1),
+                           "pct_hbm_measured_per_gpu": round(by_gpu / us / 1e3 / peaks["hbm_gbs"] * 100, 1),
+                           "n_local": nl0, "path": "mn_small" if path == f.PATH_MN_SMALL else "mn_large",
+                           "splits": splits, "tile_n": tile_n, "e2e_us": round(e, 1)})
     dom = SHAPES_18.index(DOMINANT)
-    dom_tflops = 2.0 * DOMINANT[0] * DOMINANT[1] * DOMINANT[2] / per_shape_us[dom] / 1e6
+    dom_nl = plan_n_shards(DOMINANT[1], world)[0][1]
+    dom_flops = 2.0 * DOMINANT[0] * dom_nl * DOMINANT[2]                     # one launch = this GPU's column shard
+    dom_tflops = dom_flops / per_shape_us[dom] / 1e6
     fp8_peak = 2.0 * peaks["bf16_tflops"]
-    traffic = None
+    traffic, traffic_src = None, None
     try:
         with open(os.path.join(ROOT, "profiles", "dominant_kernel_traffic.json")) as fh:
-            traffic = json.load(fh).get("dram_bytes_per_launch")
+            tj = json.load(fh)
+            if world == 1:
+                traffic = tj.get("dram_bytes_per_launch")
+                traffic_src = ("not measured by this run: dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of "
+                               "this kernel on this shape, recorded in profiles/dominant_kernel_traffic.json (%s)" %
+                               tj.get("source", "see profiles/"))
     except Exception:
         pass
-    d_path, d_splits, d_tile = f.select_path(DOMINANT[0], plan_n_shards(DOMINANT[1], world)[0][1], DOMINANT[2])
+    d_path, d_splits, d_tile = f.select_path(DOMINANT[0], dom_nl, DOMINANT[2])
     d_name = ("256x256 CTA-pair tiles" if d_tile & f.TILE_PAIR else "128x%d tiles, one CTA each" % (d_tile & 0xFFF))
     roofline = {"bound": "tensor", "kernel": "gemm_kernel (%s, %s) on M=6144 N=4608 K=7168 (1/%d column shard per GPU)"
                                             % (d_name, "full K" if d_splits <= 1 else "split-K x%d" % d_splits, world),
                 "achieved": round(dom_tflops, 1), "peak": round(fp8_peak, 1), "unit": "TFLOP/s",
-                "frac": round(dom_tflops / fp8_peak, 4),
-                "peak_source": "2 x bf16_tflops (burst) of %s: fp8 issues at twice the bf16 rate; of %s" %
-                               (peak_src, "measured" if peak_src != "fallback" else "fallback"),
+                "frac": round(dom_tflops / fp8_peak, 4), "per": "GPU",
+                "peak_source": "2 x bf16_tflops (burst) of %s: fp8 issues at twice the bf16 rate; of %s" % (peak_src, of_what),
                 "frac_of_nominal_4500": round(dom_tflops / NOMINAL_FP8_TFLOPS, 4),
-                "algorithmic_flops_per_launch": 2.0 * DOMINANT[0] * DOMINANT[1] * DOMINANT[2] / world,
-                "traffic": traffic}
+                "algorithmic_flops_per_launch": dom_flops, "launch_us": round(per_shape_us[dom], 2),
+                "traffic": traffic, "traffic_source": traffic_src}
+    roofline_hbm = []
+    for shp in HBM_SHAPES:
+        i = SHAPES_18.index(shp)
+        nl0 = plan_n_shards(shp[1], world)[0][1]
+        by = algorithmic_bytes(shp[0], nl0, shp[2], shp[1])
+        gbs = by / per_shape_us[i] / 1e3
+        roofline_hbm.append({"bound": "hbm", "shape": list(shp), "n_local": nl0, "algorithmic_bytes_per_launch": by,
+                             "launch_us": round(per_shape_us[i], 2), "achieved": round(gbs, 1),
+                             "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(gbs / peaks["hbm_gbs"], 4),
+                             "per": "GPU", "peak_source": "hbm_gbs of %s (copy bandwidth); of %s" % (peak_src, of_what),
+                             "frac_of_nominal_8000": round(gbs / NOMINAL_HBM_GBS, 4)})
     cpu = cpu_sweep(16)
     line = {
         "metric": "geomean_latency_us_18_shapes", "value": round(geomean(per_shape_us), 3), "unit": "us",
@@ -501,19 +644,108 @@ def run_gpu_arm(args, rank, world):
                                "columns of B/C partitioned over %d GPU(s)" % (NK_PAIRS, world),
                    "l2": "each launch uses the next of >=3 distinct buffer sets per shape totalling > 2 x 126 MB L2, "
                          "so operands come from HBM",
-                   "launches_per_shape_per_step": "one CUDA-graph replay = one launch per buffer set"},
+                   "launches_per_shape_per_step": "one CUDA-graph replay = one launch per buffer set",
+                   "value_is": "mean over replays of (replay time / launches in it): back-to-back launches whose prologues "
+                               "overlap the previous kernel's tail (programmatic dependent launch); min_us / median_us / "
+                               "isolated_us per shape are in `shapes`"},
         "e2e": {"value": round(geomean(e2e_us), 2), "unit": "us", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "how": "fp8bs_gemm_host: pinned host buffers -> H2D -> kernel -> D2H -> stream sync, wall clock per call"},
-        "gpu_launches": int(gpu_launches), "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
-        "geomean_roofline_frac_note": "per-shape fractions in `shapes`",
+        "gpu_launches": int(gpu_launches), "clocks": clocks, "roofline": roofline, "roofline_hbm": roofline_hbm,
+        "parity": parity, "cpu_baseline": cpu,
+        "geomean_min_us": round(geomean(per_shape_min), 3), "geomean_median_us": round(geomean(per_shape_med), 3),
+        "geomean_isolated_us": round(geomean(isolated), 3),
         "shapes": shapes_out,
         "m16384": {"aggregate_tflops": round(agg_flops / agg_us / 1e6, 1), "per_shape": m16},
         "allgather_c": allgather,
         "fused_c_distribution": fused,
+        "format_kernels": formats,
     }
     emit(line)
     if dist is not None:
         dist.destroy_process_group()
+
+
+def fused_distribution_leg(torch, f, h, dist, dev, rank, world, barrier, max_over_ranks, reduce_over_ranks, plan_n_shards):
+    """GEMM whose epilogue stores every tile into the full-width C of every rank (peer-mapped), timed against the
+    GEMM alone and GEMM + NCCL all-gather, and then CHECKED: every rank compares rows of its own full-width C, whose
+    columns were written by every rank, with the CPU checker.  A wrong peer store fails the run."""
+    try:
+        import torch.distributed._symmetric_memory as symm
+        M, N, K = 16384, 7168, 2304
+        plan = plan_n_shards(N, world)
+        n0, nl = plan[rank]
+        A = f.gen_normal_e4m3(M * K, 9001)
+        shards_B = [f.gen_normal_e4m3(c * K, 9002 + r) for r, (_, c) in enumerate(plan)]     # rank r's columns, [K][c]
+        a_s = f.gen_uniform_f32(M * (K // 128), 9003, 0.01, 1.0)
+        b_s = f.gen_uniform_f32(((N + 127) // 128) * (K // 128), 9004, 0.01, 1.0)
+        dA, dB = torch.from_numpy(A).to(dev), torch.from_numpy(shards_B[rank]).to(dev)
+        dAs, dBs = torch.from_numpy(a_s).to(dev), torch.from_numpy(b_s).to(dev)
+        c_full = None
+        try:
+            c_full = symm.empty((M, N), dtype=torch.bfloat16, device=dev)
+        except Exception:
+            pass
+        # every rank takes the same branch: the rendezvous and the timed loops below are collective
+        if max_over_ranks([0.0 if c_full is not None else 1.0])[0] > 0.0:
+            raise RuntimeError("symmetric memory could not be allocated on every rank")
+        hdl = symm.rendezvous(c_full, dist.group.WORLD.group_name)
+        ptrs = [int(x) for x in hdl.buffer_ptrs]
+        c_own = torch.empty((M, nl), dtype=torch.bfloat16, device=dev)
+        gathered = torch.empty((world, M, nl), dtype=torch.bfloat16, device=dev)
+
+        def timed(fn, reps=10):
+            for _ in range(3):
+                fn()
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                fn()
+            e1.record()
+            barrier()
+            return max_over_ranks([e0.elapsed_time(e1) * 1e3 / reps])[0]
+
+        def separate():
+            f.gemm(dA, dB, dAs, dBs, c_own, M, nl, K, n0=n0, n_total=N, path=f.PATH_MN_LARGE)
+            dist.all_gather_into_tensor(gathered, c_own)
+
+        t_gemm = timed(lambda: f.gemm(dA, dB, dAs, dBs, c_own, M, nl, K, n0=n0, n_total=N, path=f.PATH_MN_LARGE))
+        t_sep = timed(separate) if nl * world == N else None      # all_gather_into_tensor needs equal slabs
+        c_full.fill_(float("nan"))
+        barrier()                                                # every C is poisoned before anybody writes again
+        t_fused = timed(lambda: f.gemm_scatter(dA, dB, dAs, dBs, ptrs, M, nl, K, n0, N))
+        f.last_device_status()
+        barrier()                                                # all ranks' stores into this rank's C have drained
+        # ---- parity of the peer-written C: rows of the full-width result against the CPU checker ----
+        rows = np.unique(np.linspace(0, M - 1, FUSED_PARITY_ROWS).astype(np.int32))
+        B_full = np.concatenate([s.reshape(K, c) for s, (_, c) in zip(shards_B, plan) if c], axis=1).ravel()   # [K][N]
+        ref = h.oracle_gemm(A, B_full, a_s, b_s, M, N, K, rows=rows)
+        got = c_full.view(torch.int16)[torch.from_numpy(rows).to(dev).long()].cpu().numpy().view(np.uint16)
+        bad, first, maxerr = h.mismatches(ref, got)
+        worst = int(max_over_ranks([float(bad)])[0])
+        if worst:
+            raise AssertionError("fused distribution: %d elements of the peer-written C differ from the CPU checker on "
+                                 "some rank (this rank: %d, first at %d, max err %g)" % (worst, bad, first, maxerr))
+        link_us = (world - 1) * M * nl * 2 / 770e3
+        fused = {"shape": "M=16384 N=7168 K=2304, C row-major on every GPU", "gemm_only_us": round(t_gemm, 1),
+                 "gemm_then_nccl_all_gather_us": round(t_sep, 1) if t_sep else None,
+                 "gemm_with_fused_distribution_us": round(t_fused, 1),
+                 "parity_checked_rows": int(reduce_over_ranks([len(rows)], "sum")[0]),
+                 "parity": "each of the %d ranks compared %d rows x all %d columns of its own C (columns written by every "
+                           "rank through peer stores) with the CPU checker: 0 mismatches" % (world, len(rows), N),
+                 "roofline": {"bound": "slower of the GEMM alone and the peer bytes over one NVLink direction (770 GB/s measured peer copy)",
+                              "target_us": round(max(t_gemm, link_us), 1),
+                              "frac": round(max(t_gemm, link_us) / t_fused, 3)},
+                 "note": "all-gather leaves [rank][M][N/ranks] slabs that still need a re-layout pass; the fused "
+                         "epilogue writes row-major M x N directly; peer bytes per GPU %.0f MB" %
+                         ((world - 1) * M * nl * 2 / 1e6)}
+        barrier()
+        del c_full, hdl
+        return fused
+    except AssertionError:
+        raise
+    except Exception as exc:                                   # symmetric memory unavailable on this box
+        return {"unavailable": str(exc)[:300]}
 
 
 _JSON_FD = None

@@ -26,6 +26,7 @@ from .api import (  # noqa: F401
     quantize_block,
     HostContext,
     select_path,
+    select_path_sms,
     workspace_bytes,
     gen_normal_e4m3,
     gen_uniform_f32,

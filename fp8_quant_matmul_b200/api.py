@@ -40,6 +40,7 @@ _SIGS = {
     "fp8bs_gemm_scatter": (_c.c_int, [_c.c_void_p] * 4 + [_c.POINTER(_c.c_void_p)] + [_c.c_int] * 6 + [_c.c_void_p]),
     "fp8bs_gemm_ref": (_c.c_int, [_c.c_void_p] * 5 + [_c.c_int] * 3 + [_c.c_void_p]),
     "fp8bs_select_path": (_c.c_int, [_c.c_int] * 3 + [_c.POINTER(_c.c_int)] * 2),
+    "fp8bs_select_path_sms": (_c.c_int, [_c.c_int] * 4 + [_c.POINTER(_c.c_int)] * 3),
     "fp8bs_workspace_bytes": (_c.c_size_t, [_c.c_int] * 3),
     "fp8bs_workspace_bytes_ex": (_c.c_size_t, [_c.c_int] * 6),
     "fp8bs_workspace_init": (_c.c_int, [_c.c_void_p, _c.c_size_t, _c.c_void_p]),
@@ -109,6 +110,15 @@ def select_path(M, N, K):
     if rc < 0:
         raise Fp8bsError(rc, "fp8bs_select_path")
     return rc, s.value, t.value
+
+
+def select_path_sms(M, N, K, sm_count):
+    """(path, splits, tile_n, ctas that must be co-resident) for a GPU with sm_count SMs (pure host function)."""
+    s, t, c = _c.c_int(0), _c.c_int(0), _c.c_int(0)
+    rc = lib().fp8bs_select_path_sms(M, N, K, sm_count, _c.byref(s), _c.byref(t), _c.byref(c))
+    if rc < 0:
+        raise Fp8bsError(rc, "fp8bs_select_path_sms")
+    return rc, s.value, t.value, c.value
 
 
 def workspace_bytes(M, N, K, path=None, splits=0, tile_n=0):

@@ -1,8 +1,15 @@
 """Builds libfp8bs.so (the CUDA kernels + C ABI) and the C++ harness programs in-tree.
 
-    python -m fp8_quant_matmul_b200.build [--force]
+    python -m fp8_quant_matmul_b200.build [--force] [-v] [--profile[=LEVEL]]
 
 nvcc cross-compiles for sm_100a, so this works on a machine without a GPU.
+
+--profile additionally builds lib/libfp8bs_prof.so, the same library compiled with -DFP8BS_PROFILE=LEVEL
+(1: per-CTA time stamps of the kernel's phases; 2: plus cycle counters around every barrier wait; 3, the default:
+plus a per-K-block time line of CTA 0).  The instrumented kernels write into a buffer that the extra export
+fp8bs_debug_prof(long long* out, int n) copies back; csrc/gemm_kernel.cuh documents its layout.  The timers perturb
+what they measure (a K block costs 10-15 % more), so that library is for finding out where time goes, never for
+timing; nothing else in the package loads it.
 """
 import os
 import shutil
@@ -60,6 +67,14 @@ def build_library(force=False, verbose=False):
     return LIB_PATH
 
 
+def build_profile_library(level=3):
+    """Compile the instrumented variant lib/libfp8bs_prof.so (see the module docstring)."""
+    os.makedirs(LIB_DIR, exist_ok=True)
+    out = os.path.join(LIB_DIR, "libfp8bs_prof.so")
+    _run([_nvcc()] + NVCC_FLAGS + ["-DFP8BS_PROFILE=%d" % int(level), "-shared", "-o", out, os.path.join(CSRC, "fp8bs.cu")])
+    return out
+
+
 def build_programs(force=False):
     """Compile the C++ harness programs host/check.cpp and host/sgemm.cpp into bin/."""
     built = []
@@ -88,5 +103,8 @@ def build_all(force=False, verbose=False):
 if __name__ == "__main__":
     lib, progs = build_all(force="--force" in sys.argv, verbose="-v" in sys.argv)
     print(lib)
+    for arg in sys.argv[1:]:
+        if arg.startswith("--profile"):
+            print(build_profile_library(int(arg.split("=")[1]) if "=" in arg else 3))
     for p in progs:
         print(p)

@@ -48,10 +48,35 @@ constexpr size_t COUNTER_BYTES = 65536;            // head of the workspace: 163
 constexpr int MAX_SPLITS = 32;
 constexpr size_t BSCALE_MAX_BYTES = 4u << 20;     // b_scale staging of the end-to-end context
 
+// What the dispatch needs to know about a GPU: how many SMs, and how many thread-block clusters of each size
+// (one CTA per SM, this library's shared-memory footprint) can be resident at once.
+struct DeviceModel {
+    int sm_count;
+    int max_clusters[9];
+};
+// A full B200: 148 SMs; cudaOccupancyMaxActiveClusters for the split-K kernel gives 148/74/45/33/26/22/15/15 for
+// cluster sizes 1..8.  Used when no device has been set up (the pure host functions on a machine without a GPU).
+static const DeviceModel kB200Model = {148, {0, 148, 74, 45, 33, 26, 22, 15, 15}};
+
+// The model of a GPU with `sm_count` SMs when it cannot be asked: the B200 table scaled by the SM count.
+static DeviceModel scaled_model(int sm_count)
+{
+    DeviceModel m = kB200Model;
+    if (sm_count > 0 && sm_count != kB200Model.sm_count) {
+        m.sm_count = sm_count;
+        for (int s = 1; s <= 8; ++s) {
+            m.max_clusters[s] = kB200Model.max_clusters[s] * sm_count / kB200Model.sm_count;
+            if (m.max_clusters[s] < 1 && s <= sm_count) m.max_clusters[s] = 1;
+        }
+    }
+    return m;
+}
+
 struct DeviceInfo {
     bool ready = false;
     int status = FP8BS_OK;
     int sm_count = 0;
+    DeviceModel model = kB200Model;
     unsigned int* status_ptr = nullptr;            // device address of g_device_status
     void* static_scratch = nullptr;                // device address of g_static_scratch (looked up on first use)
 };
@@ -72,7 +97,7 @@ template <int BN, int CG, int MODE>
 static int prepare_kernel()
 {
     CUDA_TRY(cudaFuncSetAttribute(gemm_kernel<BN, CG, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  TileCfg<BN, CG>::SMEM_BYTES));
+                                  TileCfg<BN, CG, MODE>::SMEM_BYTES));
     return FP8BS_OK;
 }
 
@@ -123,6 +148,24 @@ static int device_setup(DeviceInfo** out)
             return d.status;
         }
         d.status_ptr = static_cast<unsigned int*>(sp);
+        // cluster occupancy of the split-K kernel on this device (both tile widths have the same footprint)
+        d.model = scaled_model(d.sm_count);
+        for (int cs = 1; cs <= 8; ++cs) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(static_cast<unsigned>(cs * 64), 1, 1);
+            cfg.blockDim = dim3(TileCfg<128, 1, 2>::THREADS, 1, 1);
+            cfg.dynamicSmemBytes = TileCfg<128, 1, 2>::SMEM_BYTES;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = static_cast<unsigned>(cs);
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, gemm_kernel<128, 1, 2>, &cfg) == cudaSuccess && n > 0) d.model.max_clusters[cs] = n;
+            else (void)cudaGetLastError();
+        }
         if (cudaMemset(sp, 0, sizeof(unsigned int) * 4) != cudaSuccess) {
             (void)cudaGetLastError();
             d.status = FP8BS_ERR_CUDA;
@@ -132,6 +175,19 @@ static int device_setup(DeviceInfo** out)
     }
     if (out) *out = &d;
     return d.status;
+}
+
+// The model the pure host functions plan with: that of the current device once a call has set it up, else a full
+// B200.  Never touches a device that has not been set up, so it works on a machine without a GPU.
+static DeviceModel host_model()
+{
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) {
+        (void)cudaGetLastError();
+        return kB200Model;
+    }
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
+    return (g_dev[dev].ready && g_dev[dev].status == FP8BS_OK) ? g_dev[dev].model : kB200Model;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -147,18 +203,17 @@ struct Config {
     int ctas;     // mode 3 only
 };
 
-constexpr int MAX_CLUSTER_SPLITS = 6;   // clusters of 7 or 8 CTAs of this size fit only 15 at a time on a B200
+constexpr int MAX_CLUSTER_SPLITS = 8;   // portable cluster size limit; 7 and 8 fit only 15 at a time on a B200
 
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
-constexpr int SM_TARGET = 148;   // B200; the dispatch is a pure function of the shape
-
-// Stream-K grid: every SM, but at least 4 K blocks per CTA.
-static int stream_k_ctas(int tiles, int KB)
+// Stream-K grid: every SM, but at least 4 K blocks per CTA.  Never more CTAs than SMs: a CTA waits (bounded) for
+// partial tiles of CTAs that must therefore be running at the same time.
+static int stream_k_ctas(int tiles, int KB, int sm_count)
 {
     const long long total = static_cast<long long>(tiles) * KB;
     long long g = total / 4;
-    if (g > SM_TARGET) g = SM_TARGET;
+    if (g > sm_count) g = sm_count;
     if (g < 1) g = 1;
     return static_cast<int>(g);
 }
@@ -174,19 +229,18 @@ static int stream_k_ctas(int tiles, int KB)
 //   cudaOccupancyMaxActiveClusters for this kernel's footprint (one CTA per SM), tabulated below for a B200;
 //   overhead 2 us (3 us for 256-wide tiles) + 0.5 us per split and 128 columns (shared-memory round trip, two
 //   cluster barriers), paid again with 3 us of prologue by every further wave of clusters.
-static const int kMaxActiveClusters[9] = {0, 148, 74, 45, 33, 26, 22, 15, 15};
 // Stream-K hand-over per 128 columns of tile width: a CTA first leaves a partial tile in the workspace (its promotion
 // warps are busy with that while its MMA warp runs dry) and at the end reads its neighbours'; CTAs that run side by side
 // are also on tiles far apart and share less through L2.  Measured 6-11 us in total on the benchmark shapes, which
 // is why the estimate keeps stream-K for shapes with very few, very long tiles only.
 constexpr double STREAM_K_FIXUP_US = 6.0;
-static double config_cost(int M, int N, int K, int tile_n, int splits, int cg, int mode)
+static double config_cost(const DeviceModel& dm, int M, int N, int K, int tile_n, int splits, int cg, int mode)
 {
     const int KB = K / 128;
     const int tiles = ceil_div(M, 128 * cg) * ceil_div(N, tile_n);
     if (mode == 3) {
         // every CTA: ceil(T / G) K blocks, its share of the tile switches, one partial-sum hand-over each way
-        const int g = stream_k_ctas(tiles, KB);
+        const int g = stream_k_ctas(tiles, KB, dm.sm_count);
         const long long total = static_cast<long long>(tiles) * KB;
         const double kb_each = static_cast<double>((total + g - 1) / g);
         const double per_kb3 = (tile_n == 256 ? 0.53 : 0.44), per_unit3 = (tile_n == 256 ? 1.2 : 0.35);
@@ -196,7 +250,8 @@ static double config_cost(int M, int N, int K, int tile_n, int splits, int cg, i
                STREAM_K_FIXUP_US * (tile_n / 128) * (sharers / 2.0);
     }
     const int units = tiles * splits;
-    const int waves = (mode == 2) ? ceil_div(tiles, kMaxActiveClusters[splits]) : ceil_div(units, SM_TARGET / cg);
+    if (dm.sm_count < cg || (mode == 2 && dm.max_clusters[splits] < 1)) return 1e300;   // cannot run on this device
+    const int waves = (mode == 2) ? ceil_div(tiles, dm.max_clusters[splits]) : ceil_div(units, dm.sm_count / cg);
     const double per_kb = (cg == 2) ? 0.60 : (tile_n == 256 ? 0.53 : 0.44);
     const double per_unit = (cg == 2) ? 2.0 : (tile_n == 256 ? 1.2 : 0.35);
     double cost = 3.5 + waves * (ceil_div(KB, splits) * per_kb + per_unit);
@@ -215,7 +270,7 @@ static double config_cost(int M, int N, int K, int tile_n, int splits, int cg, i
 // tile_n argument of the API: 0 = choose; 128 or 256 = tile width, one CTA per tile;
 // 256 | FP8BS_TILE_PAIR = 256 x 256 tile owned by a pair of CTAs; | FP8BS_SPLIT_WORKSPACE = reduce split-K partial
 // sums through the workspace even where the cluster reduction could be used.
-static Config choose_config(int M, int N, int K, int path, int splits, int tile_n)
+static Config choose_config(const DeviceModel& dm, int M, int N, int K, int path, int splits, int tile_n)
 {
     const int KB = K / 128;
     const bool force_ws = (tile_n & FP8BS_SPLIT_WORKSPACE) != 0;
@@ -231,11 +286,11 @@ static Config choose_config(int M, int N, int K, int path, int splits, int tile_
             const int tiles = ceil_div(M, 128) * ceil_div(N, tn);
             // With more tiles than SMs the CTAs that run side by side are on tiles far apart and share little
             // through L2 (measured: 369 us against 186 us on 16384 x 1536 x 7168): only on request there.
-            if (!force_sk && tiles > SM_TARGET) continue;
-            const double c = config_cost(M, N, K, tn, 1, 1, 3);
+            if (!force_sk && tiles > dm.sm_count) continue;
+            const double c = config_cost(dm, M, N, K, tn, 1, 1, 3);
             if (c < best_cost) {
                 best_cost = c;
-                best = Config{FP8BS_PATH_MN_SMALL, tn, 1, 1, 3, stream_k_ctas(tiles, KB)};
+                best = Config{FP8BS_PATH_MN_SMALL, tn, 1, 1, 3, stream_k_ctas(tiles, KB, dm.sm_count)};
             }
         }
         if (force_sk) return best;
@@ -248,9 +303,10 @@ static Config choose_config(int M, int N, int K, int path, int splits, int tile_
             for (int s = 1; s <= smax; ++s) {
                 if (splits && s != splits) continue;
                 const bool small = (s > 1 || path == FP8BS_PATH_MN_SMALL);
-                const bool cluster_ok = small && cg == 1 && s >= 2 && s <= MAX_CLUSTER_SPLITS && !force_ws;
+                const bool cluster_ok = small && cg == 1 && s >= 2 && s <= MAX_CLUSTER_SPLITS && !force_ws &&
+                                        dm.max_clusters[s] > 0;
                 for (int mode = small ? 1 : 0; mode <= (cluster_ok ? 2 : (small ? 1 : 0)); ++mode) {
-                    const double c = config_cost(M, N, K, tn, s, cg, mode);
+                    const double c = config_cost(dm, M, N, K, tn, s, cg, mode);
                     if (c < best_cost) {
                         best_cost = c;
                         best = Config{small ? FP8BS_PATH_MN_SMALL : FP8BS_PATH_MN_LARGE, tn, s, cg, mode, 0};
@@ -359,11 +415,11 @@ struct TensorMaps {
 template <int BN, int CG, int MODE>
 static int launch(const TensorMaps& tm, const GemmParams& p, int sm_count, cudaStream_t stream)
 {
-    using Cfg = TileCfg<BN, CG>;
+    using Cfg = TileCfg<BN, CG, MODE>;
     const int units = p.m_tiles * p.n_tiles * p.splits;
     int groups = units < sm_count / CG ? units : sm_count / CG;    // tile walkers: CTAs or CTA pairs
     if (MODE == 2) groups = units;                                  // one CTA per (tile, K range); a cluster per tile
-    if (MODE == 3) groups = stream_k_ctas(p.m_tiles * p.n_tiles, p.K / 128);
+    if (MODE == 3) groups = stream_k_ctas(p.m_tiles * p.n_tiles, p.K / 128, sm_count);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(groups * CG), 1, 1);
     cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
@@ -422,7 +478,12 @@ static int gemm_impl(const void* A, const void* B, const float* a_scale, const f
         return FP8BS_ERR_ALIGN;
     if ((reinterpret_cast<uintptr_t>(a_scale) & 15u) || (reinterpret_cast<uintptr_t>(b_scale) & 3u)) return FP8BS_ERR_ALIGN;
 
-    Config cfg = choose_config(M, N, K, path, splits, tile_n);
+    // The device is set up before the dispatch decides (its SM count and cluster occupancy go into the decision),
+    // but a failure here is only reported once the remaining argument and workspace checks have passed.
+    DeviceInfo* dev = nullptr;
+    const int dev_rc = device_setup(&dev);
+    const DeviceModel dm = (dev_rc == FP8BS_OK) ? dev->model : kB200Model;
+    Config cfg = choose_config(dm, M, N, K, path, splits, tile_n);
     if (dests && cfg.mode == 2) return FP8BS_ERR_ARG;       // the cluster reduction stores C itself, to one buffer
     if (cfg.mode == 1 || cfg.mode == 3) {
         const size_t need = config_workspace(M, N, cfg);
@@ -432,13 +493,10 @@ static int gemm_impl(const void* A, const void* B, const float* a_scale, const f
                           (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0;
         if (!fits) {
             if (path != FP8BS_PATH_AUTO || (tile_n & (FP8BS_STREAM_K | FP8BS_SPLIT_WORKSPACE))) return FP8BS_ERR_WORKSPACE;
-            cfg = choose_config(M, N, K, FP8BS_PATH_MN_LARGE, 1, tile_n);   // best full-K configuration
+            cfg = choose_config(dm, M, N, K, FP8BS_PATH_MN_LARGE, 1, tile_n);   // best full-K configuration
         }
     }
-
-    DeviceInfo* dev = nullptr;
-    rc = device_setup(&dev);
-    if (rc) return rc;
+    if (dev_rc) return dev_rc;
 
     TensorMaps tm{};
     if ((rc = encode_operand_map(&tm.A, A, M, K))) return rc;
@@ -652,7 +710,7 @@ int fp8bs_gemm_mn_small_static(const void* A, const void* B, const float* a_scal
     int rc = check_args(M, N, K, 0, N, FP8BS_PATH_MN_SMALL, splits, 0);
     if (rc) return rc;
     // refuse anything the built-in scratch cannot hold, before touching the device
-    const Config cfg = choose_config(M, N, K, FP8BS_PATH_MN_SMALL, splits, FP8BS_SPLIT_WORKSPACE);
+    const Config cfg = choose_config(host_model(), M, N, K, FP8BS_PATH_MN_SMALL, splits, FP8BS_SPLIT_WORKSPACE);
     if (config_workspace(M, N, cfg) > STATIC_SCRATCH_BYTES) return FP8BS_ERR_WORKSPACE;
     DeviceInfo* dev = nullptr;
     rc = device_setup(&dev);                       // first call on a device: attribute set-up, no allocation
@@ -694,23 +752,40 @@ int fp8bs_select_path(int M, int N, int K, int* splits, int* tile_n)
 {
     const int rc = check_shape(M, N, K);
     if (rc) return rc;
-    const Config c = choose_config(M, N, K, FP8BS_PATH_AUTO, 0, 0);
+    const Config c = choose_config(host_model(), M, N, K, FP8BS_PATH_AUTO, 0, 0);
     if (splits) *splits = c.splits;
     if (tile_n) *tile_n = c.tile_n | (c.cg == 2 ? FP8BS_TILE_PAIR : 0) | (c.mode == 1 ? FP8BS_SPLIT_WORKSPACE : 0) |
                           (c.mode == 3 ? FP8BS_STREAM_K : 0);
     return c.path;
 }
 
+int fp8bs_select_path_sms(int M, int N, int K, int sm_count, int* splits, int* tile_n, int* ctas)
+{
+    const int rc = check_shape(M, N, K);
+    if (rc) return rc;
+    if (sm_count < 1) return FP8BS_ERR_ARG;
+    const Config c = choose_config(scaled_model(sm_count), M, N, K, FP8BS_PATH_AUTO, 0, 0);
+    if (splits) *splits = c.splits;
+    if (tile_n) *tile_n = c.tile_n | (c.cg == 2 ? FP8BS_TILE_PAIR : 0) | (c.mode == 1 ? FP8BS_SPLIT_WORKSPACE : 0) |
+                          (c.mode == 3 ? FP8BS_STREAM_K : 0);
+    if (ctas) {
+        // CTAs that have to be resident together: stream-K's whole grid, one cluster for the cluster reduction,
+        // otherwise none (the tile walkers never wait on one another)
+        *ctas = (c.mode == 3) ? c.ctas : (c.mode == 2 ? c.splits : 0);
+    }
+    return c.path;
+}
+
 size_t fp8bs_workspace_bytes(int M, int N, int K)
 {
     if (check_shape(M, N, K)) return 0;
-    return config_workspace(M, N, choose_config(M, N, K, FP8BS_PATH_AUTO, 0, 0));
+    return config_workspace(M, N, choose_config(host_model(), M, N, K, FP8BS_PATH_AUTO, 0, 0));
 }
 
 size_t fp8bs_workspace_bytes_ex(int M, int N, int K, int path, int splits, int tile_n)
 {
     if (check_args(M, N, K, 0, N, path, splits, tile_n)) return 0;
-    return config_workspace(M, N, choose_config(M, N, K, path, splits, tile_n));
+    return config_workspace(M, N, choose_config(host_model(), M, N, K, path, splits, tile_n));
 }
 
 int fp8bs_workspace_init(void* workspace, size_t workspace_bytes, void* stream)
@@ -727,12 +802,13 @@ int fp8bs_last_device_status(void* stream, unsigned int* detail)
     const int rc = device_setup(&dev);
     if (rc) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    CUDA_TRY(cudaStreamSynchronize(st));
+    // read, and if needed clear, on the caller's stream: nothing here orders or blocks other streams
     unsigned int word = 0;
-    CUDA_TRY(cudaMemcpy(&word, dev->status_ptr, sizeof(word), cudaMemcpyDeviceToHost));
+    CUDA_TRY(cudaMemcpyAsync(&word, dev->status_ptr, sizeof(word), cudaMemcpyDeviceToHost, st));
+    CUDA_TRY(cudaStreamSynchronize(st));
     if (detail) *detail = word;
     if (word != 0) {
-        CUDA_TRY(cudaMemset(dev->status_ptr, 0, sizeof(word)));
+        CUDA_TRY(cudaMemsetAsync(dev->status_ptr, 0, sizeof(word), st));
         return FP8BS_ERR_DEVICE_TIMEOUT;
     }
     return FP8BS_OK;

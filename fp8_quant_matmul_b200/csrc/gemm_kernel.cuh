@@ -14,7 +14,7 @@
 //           1, 2 "mn_small": every tile is cut into `splits` K ranges and the partial sums are
 //                 added in split order 0..S-1, so the result does not depend on timing (replaces
 //                 k_large_kernel, mn_small.hip:10-137, which instead shrinks the tile to get more
-//                 blocks).  MODE 2 (S <= 8; the host uses it up to 6): the S CTAs of a tile form a
+//                 blocks).  MODE 2 (S <= 8): the S CTAs of a tile form a
 //                 thread-block cluster, each leaves its fp32 partial tile in its own shared memory,
 //                 and after a cluster barrier every CTA reduces 128/S rows straight out of its
 //                 peers' shared memory (DSMEM): no workspace, no atomics.  MODE 1 (any S, also pair
@@ -101,7 +101,7 @@ struct GemmParams {
 // otherwise unchanged: a per-block hand-off cost ~160 cycles per K block of a loop that has ~512 to spend.
 constexpr int SCALE_GROUP = 8;
 
-template <int BN, int CG>
+template <int BN, int CG, int MODE = 0>
 struct TileCfg {
     static_assert(BN == 128 || BN == 256, "tile width");
     static_assert(CG == 1 || (CG == 2 && BN == 256), "pair tiles are 256 x 256");
@@ -123,7 +123,9 @@ struct TileCfg {
     // a thread's 128 columns), so the second half need not wait for the first store to drain; pair tiles, used for long
     // K where the epilogue is a small part, keep one box and the extra pipeline stage instead.
     static constexpr int NSTG = (CG == 1) ? COLS / 64 : 1;
-    static constexpr int STG_BYTES = PROMO_WARPS * 4096 * NSTG;
+    // MODE 2 (cluster split-K) writes C with plain stores after the reduction: no staging boxes, so the shared memory
+    // buys one more pipeline stage, which these load-latency-bound configurations need most
+    static constexpr int STG_BYTES = (MODE == 2) ? 0 : PROMO_WARPS * 4096 * NSTG;
     static constexpr int SGRP = SCALE_GROUP;          // K blocks per a_scale ring entry (one TMA box {128 rows, SGRP})
     static constexpr int SRING = 4;                   // a_scale ring entries
     static constexpr int SRING_BYTES = SRING * SGRP * 512;
@@ -138,9 +140,20 @@ struct TileCfg {
 
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;  // about one second
 
+// Instrumentation, compiled in only by `python -m fp8_quant_matmul_b200.build --profile[=LEVEL]` (-DFP8BS_PROFILE=LEVEL,
+// into a separate libfp8bs_prof.so).  Layout of the buffer GemmParams::prof points to, in 64-bit words:
+//   [cta * 16 + slot]           slots 0-7 cycle counters (level >= 2): producer wait for a free stage, MMA wait for a
+//                               free TMEM buffer, MMA wait for operands, MMA loop total, promotion wait for a_scale,
+//                               promotion wait for partial sums, promotion loads + FMAs, epilogue;
+//                               slots 8-14 %globaltimer stamps in ns: kernel start, set-up done, first operands
+//                               there, MMA loop done, promotion loop done, all stores issued, exit; slot 15 the
+//                               CTA's lifetime in cycles
+//   [4096 + event * 128 + kb]   level 3, CTA 0, first 128 K blocks, clock64 at: 0 TMEM buffer free (MMA warp),
+//                               1 operands there, 2 MMAs and commits issued, 3 a_scale there (promotion warp 4),
+//                               4 partial sums there, 5 FMAs done, 6 stage free (producer), 7 / 8 = 4 / 5 for warp 5
 #ifdef FP8BS_PROFILE
 #define PROF_DECL(name) long long name = 0
-#if FP8BS_PROFILE >= 2   // per-wait timers: they perturb the loops they measure
+#if FP8BS_PROFILE >= 2 && !defined(FP8BS_PROFILE_NOTIMERS)   // per-wait timers: they perturb the loops they measure
 #define PROF_T0() const long long prof_t0__ = clock64()
 #define PROF_ADD(name) name += clock64() - prof_t0__
 #else
@@ -265,12 +278,51 @@ __global__ void wait_timeout_selftest_kernel(unsigned int* status, long long lim
     (void)ok;
 }
 
+// Cluster split-K, final step: this CTA finishes rows [r0, r1) of the tile.  Every element is the sum of the S partial
+// tiles in the order 0, 1, .., S-1 (bit-deterministic), read out of the S CTAs' shared memory (peer[s] = cluster
+// address of CTA s's partial tile, rows of `pitch` bytes).  A remote shared-memory load takes several hundred cycles,
+// so the loads of UNR items (UNR * S of them) are issued before the first sum.
+template <int BN, int S, int UNR>
+__device__ __forceinline__ void cluster_reduce_store(const uint32_t (&peer)[8], int r0, int r1, int tid, int nthreads,
+                                                     int pitch, __nv_bfloat16* C, int m0, int n0, int M, int N)
+{
+    const int items = (r1 - r0) * (BN / 4);
+    for (int base = tid; base < items; base += nthreads * UNR) {
+        float4 v[UNR][S];
+#pragma unroll
+        for (int j = 0; j < UNR; ++j) {
+            const int idx = base + j * nthreads;
+            if (idx < items) {
+                const uint32_t off = static_cast<uint32_t>((r0 + idx / (BN / 4)) * pitch + (idx % (BN / 4)) * 16);
+#pragma unroll
+                for (int s = 0; s < S; ++s) v[j][s] = ptx::ld_shared_cluster_v4(peer[s] + off);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < UNR; ++j) {
+            const int idx = base + j * nthreads;
+            if (idx < items) {
+                float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+                for (int s = 0; s < S; ++s) { sum.x += v[j][s].x; sum.y += v[j][s].y; sum.z += v[j][s].z; sum.w += v[j][s].w; }
+                const int m = m0 + r0 + idx / (BN / 4), n = n0 + (idx % (BN / 4)) * 4;
+                if (m < M && n < N) {
+                    uint2 q;
+                    q.x = pack_bf16x2(sum.x, sum.y);
+                    q.y = pack_bf16x2(sum.z, sum.w);
+                    *reinterpret_cast<uint2*>(C + static_cast<size_t>(m) * N + n) = q;
+                }
+            }
+        }
+    }
+}
+
 template <int BN, int CG, int MODE>
-__global__ void __launch_bounds__(TileCfg<BN, CG>::THREADS, 1)
+__global__ void __launch_bounds__(TileCfg<BN, CG, MODE>::THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmAs, const __grid_constant__ CMaps cmaps, const GemmParams p)
 {
-    using Cfg = TileCfg<BN, CG>;
+    using Cfg = TileCfg<BN, CG, MODE>;
     constexpr int STAGES = Cfg::STAGES;
     constexpr int NBUF = Cfg::NBUF;
     constexpr int SRING = Cfg::SRING;
@@ -437,9 +489,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 const long long t0 = clock64();
                 while (clock64() - t0 < 2000000LL) __nanosleep(1000);
             }
-        } else if (warp == 1 && lane == 0 && rank == 0) {
+        } else if ((warp == 1 || (CG == 1 && warp == 3)) && lane == 0 && rank == 0) {
             // ---------------------------------------------------- MMA issuer ----------------
             constexpr uint32_t idesc = ptx::make_idesc_e4m3_mnmajor(Cfg::TILE_M, BN);
+            constexpr uint32_t n_issuers = (CG == 1) ? 2u : 1u;
+            const uint32_t my_issuer = (warp == 1) ? 0u : 1u;
             uint32_t it = 0, ait = 0;
             bool ok = true;
             PROF_DECL(w_tempty); PROF_DECL(w_full); PROF_DECL(t_mma_total);
@@ -452,6 +506,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 int tile, m0, n0, kb0, kb1;
                 decode(u, tile, m0, n0, kb0, kb1);
                 for (int kb = kb0; kb < kb1; ++kb, ++it, ++ait) {
+                    if (n_issuers > 1 && (it % n_issuers) != my_issuer) continue;
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1u;
                     const int b = ait % NBUF;
@@ -519,6 +574,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             }
         }
         __syncwarp();
+        if constexpr (MODE == 2) {           // the barriers around the cluster reduction (done by the promotion warps)
+            __syncthreads();
+            ptx::cluster_sync();
+        }
     } else {
         // -------------------------------------------------------- promotion + epilogue ------
         ptx::setmaxnreg_inc<216>();
@@ -534,6 +593,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         uint32_t sgit = 0;                       // a_scale ring entries consumed so far
         bool ok = true;
         PROF_DECL(w_sfull); PROF_DECL(w_tfull); PROF_DECL(t_fma); PROF_DECL(t_epi);
+        // b_scale lane vectors of unit u: K blocks kb0 + lane and kb0 + 32 + lane of the one or two 128-column blocks
+        // this thread's columns fall into (same index arithmetic as at the top of the unit loop)
+        float pf_bl = 0.0f, pf_bh = 0.0f, pf_bln = 0.0f, pf_bhn = 0.0f;
+        auto fetch_bscale = [&](int u) {
+            int tile, m0, n0, kb0, kb1;
+            decode(u, tile, m0, n0, kb0, kb1);
+            const int g0 = p.n_off + n0 + grp * Cfg::COLS;
+            int lo = g0 >> 7, hi = (g0 >> 7) + 1;
+            lo = lo < p.sn ? lo : p.sn - 1;
+            hi = hi < p.sn ? hi : p.sn - 1;
+            auto ld = [&](int nb, int kbase) {
+                const int k = kbase + lane;
+                return (k < kb1) ? __ldg(p.b_scale + nb + static_cast<size_t>(k) * p.sn) : 0.0f;
+            };
+            pf_bl = ld(lo, kb0);
+            pf_bh = ld(hi, kb0);
+            pf_bln = ld(lo, kb0 + 32);
+            pf_bhn = ld(hi, kb0 + 32);
+        };
+        if (unit0 < units) fetch_bscale(unit0);
         for (int u = unit0; u < units; u += unit_step) {
             int tile, m0, n0, kb0, kb1;
             decode(u, tile, m0, n0, kb0, kb1);
@@ -552,15 +631,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 for (int i = 0; i < 16; ++i) acc[c][i] = 0ull;
 
             // b_scale is tiny and warp-uniform.  Lane l holds the values of K block (base + l); every 32 blocks
-            // the vector loaded one round earlier takes over, so no iteration waits on a global load.
+            // the vector loaded one round earlier takes over, so no iteration waits on a global load.  The first two
+            // vectors of a unit were fetched before the previous unit's epilogue (pf_*), so a tile switch does not
+            // wait on global memory either: with two K blocks per tile that wait was a quarter of the tile's time.
             const float* bl_ptr = p.b_scale + nb_lo;
             const float* bh_ptr = p.b_scale + nb_hi;
             auto load_bvec = [&](const float* ptr, int kbase) {
                 const int k = kbase + lane;
                 return (k < kb1) ? __ldg(ptr + static_cast<size_t>(k) * p.sn) : 0.0f;
             };
-            float bl_vec = load_bvec(bl_ptr, kb0), bh_vec = load_bvec(bh_ptr, kb0);
-            float bl_nxt = load_bvec(bl_ptr, kb0 + 32), bh_nxt = load_bvec(bh_ptr, kb0 + 32);
+            float bl_vec = pf_bl, bh_vec = pf_bh, bl_nxt = pf_bln, bh_nxt = pf_bhn;
 
             for (int kb = kb0; kb < kb1 && ok; ++kb, ++ait) {
                 const int kj = (kb - kb0) & 31;
@@ -593,6 +673,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 if (pw == 0 && lane == 0) PROF_TRACE(4, ait);
+                if (pw == 1 && lane == 0) PROF_TRACE(7, ait);
                 PROF_T0();
                 ptx::tc_fence_after_sync();
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
@@ -623,6 +704,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 // used) let the producer refill the entry before a slow warp's read had completed: rare 32-row
                 // blocks scaled with the a_scale of a later work unit.
                 if (pw == 0 && lane == 0) PROF_TRACE(5, ait);
+                if (pw == 1 && lane == 0) PROF_TRACE(8, ait);
                 const bool entry_done = (kr == Cfg::SGRP - 1) || (kb == kb1 - 1);
                 if (entry_done) {
                     __syncwarp();
@@ -631,8 +713,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 }
                 PROF_ADD(t_fma);
             }
+            if (u + unit_step < units) fetch_bscale(u + unit_step);      // in flight during the epilogue below
 #ifdef FP8BS_PROFILE
             const long long epi_start = clock64();
+            if (pw == 0 && lane == 0) PROF_TRACE(9, static_cast<uint32_t>((u - unit0) / unit_step));
             if (pw == 0 && lane == 0) { PROF_STAMP(12); }
 #endif
 
@@ -801,6 +885,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             }
 #ifdef FP8BS_PROFILE
             t_epi += clock64() - epi_start;
+            if (pw == 0 && lane == 0) PROF_TRACE(10, static_cast<uint32_t>((u - unit0) / unit_step));
 #endif
         }
 #ifdef FP8BS_PROFILE
@@ -810,39 +895,31 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         // C must have been read out of shared memory before the CTA goes away
         if (lane == 0) ptx::tma_store_wait_read<0>();
         __syncwarp();
-    }
-
-    if constexpr (MODE == 2) {
-        // ------------------------------------------------------------ cluster reduction ---
-        __syncthreads();                 // this CTA's partial tile is complete ...
-        ptx::cluster_sync();             // ... and so are those of the other K ranges of the tile
-        if (warp >= 4 && *abort_flag == 0u) {
-            const int S = p.splits;
-            const int my = static_cast<int>(ptx::cluster_ctarank());     // = this CTA's split index
-            int tile, m0, n0, kb0, kb1;
-            decode(static_cast<int>(blockIdx.x), tile, m0, n0, kb0, kb1);
-            const int r0 = (128 * my) / S, r1 = (128 * (my + 1)) / S;     // the rows this CTA finishes
-            uint32_t peer[8];
+        if constexpr (MODE == 2) {
+            // -------------------------------------------------------- cluster reduction ---
+            // (inside this branch: the code after the role branches is compiled for the small register budget of
+            // warps 0-3, and the reduction keeps dozens of remote loads in flight)
+            __syncthreads();                 // this CTA's partial tile is complete ...
+            ptx::cluster_sync();             // ... and so are those of the other K ranges of the tile
+            if (*abort_flag == 0u) {
+                const int S = p.splits;
+                const int my = static_cast<int>(ptx::cluster_ctarank());     // = this CTA's split index
+                int tile, m0, n0, kb0, kb1;
+                decode(static_cast<int>(blockIdx.x), tile, m0, n0, kb0, kb1);
+                const int r0 = (128 * my) / S, r1 = (128 * (my + 1)) / S;     // the rows this CTA finishes
+                uint32_t peer[8];
 #pragma unroll
-            for (int s = 0; s < 8; ++s) peer[s] = ptx::mapa(stage_base, static_cast<uint32_t>(s < S ? s : 0));
-            const int items = (r1 - r0) * (BN / 4);
-            for (int idx = static_cast<int>(threadIdx.x) - 128; idx < items; idx += Cfg::PROMO_THREADS) {
-                const int row = r0 + idx / (BN / 4), c4 = idx % (BN / 4);
-                const uint32_t off = static_cast<uint32_t>(row * PART_PITCH + c4 * 16);
-                float4 v[8];
-#pragma unroll
-                for (int s = 0; s < 8; ++s)
-                    if (s < S) v[s] = ptx::ld_shared_cluster_v4(peer[s] + off);
-                float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-#pragma unroll
-                for (int s = 0; s < 8; ++s)              // fixed order 0, 1, .., S-1: bit-deterministic
-                    if (s < S) { sum.x += v[s].x; sum.y += v[s].y; sum.z += v[s].z; sum.w += v[s].w; }
-                const int m = m0 + row, n = n0 + c4 * 4;
-                if (m < p.M && n < p.N) {
-                    uint2 q;
-                    q.x = pack_bf16x2(sum.x, sum.y);
-                    q.y = pack_bf16x2(sum.z, sum.w);
-                    *reinterpret_cast<uint2*>(p.C + static_cast<size_t>(m) * p.N + n) = q;
+                for (int s = 0; s < 8; ++s) peer[s] = ptx::mapa(stage_base, static_cast<uint32_t>(s < S ? s : 0));
+                const int tid = static_cast<int>(threadIdx.x) - 128;
+                switch (S) {
+                    case 1: cluster_reduce_store<BN, 1, 4>(peer, r0, r1, tid, Cfg::PROMO_THREADS, PART_PITCH, p.C, m0, n0, p.M, p.N); break;
+                    case 2: cluster_reduce_store<BN, 2, 4>(peer, r0, r1, tid, Cfg::PROMO_THREADS, PART_PITCH, p.C, m0, n0, p.M, p.N); break;
+                    case 3: cluster_reduce_store<BN, 3, 4>(peer, r0, r1, tid, Cfg::PROMO_THREADS, PART_PITCH, p.C, m0, n0, p.M, p.N); break;
+                    case 4: cluster_reduce_store<BN, 4, 4>(peer, r0, r1, tid, Cfg::PROMO_THREADS, PART_PITCH, p.C, m0, n0, p.M, p.N); break;
+                    case 5: cluster_reduce_store<BN, 5, 2>(peer, r0, r1, tid, Cfg::PROMO_THREADS, PART_PITCH, p.C, m0, n0, p.M, p.N); break;
+                    case 6: cluster_reduce_store<BN, 6, 2>(peer, r0, r1, tid, Cfg::PROMO_THREADS, PART_PITCH, p.C, m0, n0, p.M, p.N); break;
+                    case 7: cluster_reduce_store<BN, 7, 2>(peer, r0, r1, tid, Cfg::PROMO_THREADS, PART_PITCH, p.C, m0, n0, p.M, p.N); break;
+                    default: cluster_reduce_store<BN, 8, 2>(peer, r0, r1, tid, Cfg::PROMO_THREADS, PART_PITCH, p.C, m0, n0, p.M, p.N); break;
                 }
             }
         }

@@ -77,16 +77,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm,
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tm)), "r"(c0), "r"(c1), "r"(bar)
         : "memory");
 }
-// Same, with an L2 eviction-priority hint (createpolicy value).
-__device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const CUtensorMap* tm, int c0,
-                                                 int c1, uint32_t bar, uint64_t policy)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
-        " [%0], [%1, {%2, %3}], [%4], %5;"
-        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tm)), "r"(c0), "r"(c1), "r"(bar), "l"(policy)
-        : "memory");
-}
 // 2-D tiled store shared -> global (bulk-group completion).
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* tm, uint32_t src, int c0, int c1)
 {
@@ -102,11 +92,6 @@ template <int N>
 __device__ __forceinline__ void tma_store_wait_read()
 {
     asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
-}
-template <int N>
-__device__ __forceinline__ void tma_store_wait_all()
-{
-    asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
 // Makes generic-proxy writes to shared memory visible to the async proxy (TMA, tcgen05).
 __device__ __forceinline__ void fence_proxy_async_smem()
@@ -158,27 +143,6 @@ __device__ __forceinline__ void mma_commit(uint32_t bar)
                  ::"r"(bar)
                  : "memory");
 }
-// 32 lanes x 32 consecutive 32-bit columns: thread t of the warp reads lane (base lane + t).
-__device__ __forceinline__ void tmem_ld_x32(uint32_t taddr, uint32_t (&v)[32])
-{
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
-          "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
-          "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]),
-          "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]),
-          "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait()
-{
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-
 // ---------------------------------------------------------------- clusters ----------
 __device__ __forceinline__ uint32_t cluster_ctarank()
 {
@@ -213,18 +177,6 @@ __device__ __forceinline__ float4 ld_shared_cluster_v4(uint32_t cluster_addr)
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
 {
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity)
-{
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
 }
 // TMA load issued by either CTA of a pair; the byte count is reported to `bar`, which may be the
 // peer CTA's barrier (shared::cluster address).  No multicast: the data lands in this CTA only.
@@ -296,48 +248,6 @@ __device__ __forceinline__ void setmaxnreg_dec()
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
 // ---------------------------------------------------------------- promotion ---------
-// acc[0..15] += sc * cur[0..31] (two columns per instruction).
-__device__ __forceinline__ void fma32(unsigned long long (&acc)[16], const uint32_t (&cur)[32], unsigned long long sc2)
-{
-    asm volatile(
-        "{\n\t.reg .b64 t;\n\t"
-        "mov.b64 t, {%16, %17};\n\tfma.rn.f32x2 %0, t, %48, %0;\n\t"
-        "mov.b64 t, {%18, %19};\n\tfma.rn.f32x2 %1, t, %48, %1;\n\t"
-        "mov.b64 t, {%20, %21};\n\tfma.rn.f32x2 %2, t, %48, %2;\n\t"
-        "mov.b64 t, {%22, %23};\n\tfma.rn.f32x2 %3, t, %48, %3;\n\t"
-        "mov.b64 t, {%24, %25};\n\tfma.rn.f32x2 %4, t, %48, %4;\n\t"
-        "mov.b64 t, {%26, %27};\n\tfma.rn.f32x2 %5, t, %48, %5;\n\t"
-        "mov.b64 t, {%28, %29};\n\tfma.rn.f32x2 %6, t, %48, %6;\n\t"
-        "mov.b64 t, {%30, %31};\n\tfma.rn.f32x2 %7, t, %48, %7;\n\t"
-        "mov.b64 t, {%32, %33};\n\tfma.rn.f32x2 %8, t, %48, %8;\n\t"
-        "mov.b64 t, {%34, %35};\n\tfma.rn.f32x2 %9, t, %48, %9;\n\t"
-        "mov.b64 t, {%36, %37};\n\tfma.rn.f32x2 %10, t, %48, %10;\n\t"
-        "mov.b64 t, {%38, %39};\n\tfma.rn.f32x2 %11, t, %48, %11;\n\t"
-        "mov.b64 t, {%40, %41};\n\tfma.rn.f32x2 %12, t, %48, %12;\n\t"
-        "mov.b64 t, {%42, %43};\n\tfma.rn.f32x2 %13, t, %48, %13;\n\t"
-        "mov.b64 t, {%44, %45};\n\tfma.rn.f32x2 %14, t, %48, %14;\n\t"
-        "mov.b64 t, {%46, %47};\n\tfma.rn.f32x2 %15, t, %48, %15;\n\t"
-        "}"
-        : "+l"(acc[0]), "+l"(acc[1]), "+l"(acc[2]), "+l"(acc[3]), "+l"(acc[4]), "+l"(acc[5]), "+l"(acc[6]), "+l"(acc[7]), "+l"(acc[8]), "+l"(acc[9]), "+l"(acc[10]), "+l"(acc[11]), "+l"(acc[12]), "+l"(acc[13]), "+l"(acc[14]), "+l"(acc[15])
-        : "r"(cur[0]), "r"(cur[1]), "r"(cur[2]), "r"(cur[3]), "r"(cur[4]), "r"(cur[5]), "r"(cur[6]), "r"(cur[7]), "r"(cur[8]), "r"(cur[9]), "r"(cur[10]), "r"(cur[11]), "r"(cur[12]), "r"(cur[13]), "r"(cur[14]), "r"(cur[15]), "r"(cur[16]), "r"(cur[17]), "r"(cur[18]), "r"(cur[19]), "r"(cur[20]), "r"(cur[21]), "r"(cur[22]), "r"(cur[23]), "r"(cur[24]), "r"(cur[25]), "r"(cur[26]), "r"(cur[27]), "r"(cur[28]), "r"(cur[29]), "r"(cur[30]), "r"(cur[31]), "l"(sc2));
-}
-// 32 columns from TMEM, complete on return (load and wait in one statement).
-__device__ __forceinline__ void tmem_ld_x32_sync(uint32_t taddr, uint32_t (&v)[32])
-{
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n\t"
-        "tcgen05.wait::ld.sync.aligned;"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-        : "r"(taddr)
-        : "memory");
-}
-
-
 // acc[0..15] += sc * cur[0..31] (two columns per instruction), cur being a 64-column buffer.
 __device__ __forceinline__ void fma32_from64_0(unsigned long long (&acc)[16], const uint32_t (&cur)[64], unsigned long long sc2)
 {
@@ -389,7 +299,6 @@ __device__ __forceinline__ void fma32_from64_32(unsigned long long (&acc)[16], c
         : "+l"(acc[0]), "+l"(acc[1]), "+l"(acc[2]), "+l"(acc[3]), "+l"(acc[4]), "+l"(acc[5]), "+l"(acc[6]), "+l"(acc[7]), "+l"(acc[8]), "+l"(acc[9]), "+l"(acc[10]), "+l"(acc[11]), "+l"(acc[12]), "+l"(acc[13]), "+l"(acc[14]), "+l"(acc[15])
         : "r"(cur[32]), "r"(cur[33]), "r"(cur[34]), "r"(cur[35]), "r"(cur[36]), "r"(cur[37]), "r"(cur[38]), "r"(cur[39]), "r"(cur[40]), "r"(cur[41]), "r"(cur[42]), "r"(cur[43]), "r"(cur[44]), "r"(cur[45]), "r"(cur[46]), "r"(cur[47]), "r"(cur[48]), "r"(cur[49]), "r"(cur[50]), "r"(cur[51]), "r"(cur[52]), "r"(cur[53]), "r"(cur[54]), "r"(cur[55]), "r"(cur[56]), "r"(cur[57]), "r"(cur[58]), "r"(cur[59]), "r"(cur[60]), "r"(cur[61]), "r"(cur[62]), "r"(cur[63]), "l"(sc2));
 }
-
 
 // 64 columns from TMEM, complete on return (load and wait in one statement).
 __device__ __forceinline__ void tmem_ld_x64_sync(uint32_t taddr, uint32_t (&v)[64])

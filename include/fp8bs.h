@@ -54,9 +54,9 @@ extern "C" {
 /* tile_n values: 0 = let the library choose; 128 or 256 = tile width with one CTA per 128-row tile;
  * 256 | FP8BS_TILE_PAIR = a 256 x 256 tile owned by a pair of CTAs (tcgen05 cta_group::2). */
 #define FP8BS_TILE_PAIR      0x1000
-/* Split-K partial sums are normally reduced inside a thread-block cluster through shared memory (2..6 splits, one
+/* Split-K partial sums are normally reduced inside a thread-block cluster through shared memory (2..8 splits, one
  * CTA per tile): no workspace is needed then.  OR this flag into tile_n to reduce through the workspace instead
- * (always used for more than 6 splits and for pair tiles). */
+ * (always used for more than 8 splits and for pair tiles). */
 #define FP8BS_SPLIT_WORKSPACE 0x2000
 /* Stream-K: the 128-K blocks of all tiles are dealt out evenly over the SMs, so the run time does not jump with the
  * tile count; a tile whose blocks fall to two or more CTAs is finished by the CTA that holds its first block, from
@@ -80,7 +80,7 @@ int fp8bs_gemm_mn_large(const void* A, const void* B, const float* a_scale, cons
                         void* C, int M, int N, int K, void* stream);
 
 /* Forced small-M.N / large-K path: replaces k_large_kernel<<<grid, block>>> (mn_small.hip:10;
- * launch at check.cu:92-101).  splits = 0 lets the library choose; 1 <= splits <= K/128.
+ * launch at check.cu:92-101).  splits = 0 lets the library choose; 1 <= splits <= min(K/128, 32).
  * Partial sums are added in split order, so repeated calls give bit-identical C.  The workspace is only used
  * where fp8bs_workspace_bytes_ex reports a non-zero size for the configuration (may be NULL otherwise). */
 int fp8bs_gemm_mn_small(const void* A, const void* B, const float* a_scale, const float* b_scale,
@@ -136,6 +136,11 @@ int fp8bs_gemm_ref(const void* A, const void* B, const float* a_scale, const flo
  * FP8BS_PATH_MN_SMALL (or a negative error) and stores the split count and tile width
  * (either pointer may be NULL).  Replaces the geometry switch of check.cu:86-117. */
 int fp8bs_select_path(int M, int N, int K, int* splits, int* tile_n);
+/* The same decision for a GPU with `sm_count` SMs (fp8bs_select_path plans for the current device once a call has
+ * set it up, and for a full B200 -- 148 SMs -- before that or without a GPU).  *ctas (optional) receives the number
+ * of CTAs the chosen configuration needs resident at the same time: the whole grid for stream-K, one cluster for the
+ * cluster reduction, 0 otherwise; it never exceeds sm_count. */
+int fp8bs_select_path_sms(int M, int N, int K, int sm_count, int* splits, int* tile_n, int* ctas);
 
 /* Workspace the auto dispatch wants for this shape (0 if it would not split K), and the
  * same for an explicit configuration.  The workspace must be zeroed once with

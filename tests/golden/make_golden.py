@@ -1,7 +1,7 @@
-"""Generates the golden fixtures in this directory.  Run once, in a checkout that has the
-reference sources mounted (default /root/reference) and oracle/_ref built:
+"""Generates the golden fixtures in this directory.  Run once, on a machine that has a checkout of the
+reference project, after `make -C oracle REF=/path/to/reference` has built oracle/_ref:
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
 The reference stores no expected outputs for its operator, so every fixture here is an
 output of reference CODE run on seeded inputs:
@@ -29,7 +29,9 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) != 2 or not os.path.isfile(os.path.join(sys.argv[1], "quantize.py")):
+    raise SystemExit("usage: python tests/golden/make_golden.py /path/to/reference   (the checkout that holds quantize.py)")
+REF = sys.argv[1]
 sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "tests"))
 import helpers  # noqa: E402

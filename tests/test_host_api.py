@@ -188,3 +188,24 @@ def test_stream_k_is_never_chosen_above_one_wave_of_tiles():
                     assert (f.workspace_bytes(M, nl, K) > 0) == bool(tile_n & (f.SPLIT_WORKSPACE | f.STREAM_K))
     # forcing it is always possible, and it then reports its workspace
     assert f.workspace_bytes(16384, 1536, 7168, f.PATH_MN_SMALL, 1, 256 | f.STREAM_K) == 65536 + 148 * 256 * 128 * 4
+
+
+def test_dispatch_for_a_smaller_gpu_never_needs_more_resident_ctas_than_sms():
+    # stream-K CTAs wait (bounded) for partial tiles of other CTAs and the CTAs of a cluster wait for each other at a
+    # hardware barrier: both need all of them resident together, whatever the SM count the context exposes
+    from fp8_quant_matmul_b200.shard import plan_n_shards
+    shapes = set()
+    for M in (1024, 6144):
+        for (N, K) in ((1536, 7168), (576, 7168), (7168, 256), (4608, 7168), (512, 7168), (4096, 512)):
+            for g in (1, 8):
+                shapes |= {(M, nl, K) for (_, nl) in plan_n_shards(N, g)}
+    for sms in (148, 132, 74, 36, 8, 1):
+        for (M, N, K) in sorted(shapes):
+            path, splits, tile_n, ctas = f.select_path_sms(M, N, K, sms)
+            assert ctas <= sms, (sms, M, N, K, splits, tile_n, ctas)
+            assert path in (f.PATH_MN_LARGE, f.PATH_MN_SMALL) and 1 <= splits <= K // 128
+    # a full B200 and the default model agree
+    for (M, N, K) in f.SHAPES_18:
+        assert f.select_path_sms(M, N, K, 148)[:3] == f.select_path(M, N, K)
+    with pytest.raises(f.Fp8bsError):
+        f.select_path_sms(1024, 512, 7168, 0)

@@ -62,41 +62,76 @@ def test_scatter_argument_errors():
 
 
 def _rank_main(rank, world, port, q):
+    """One rank of the peer-write test.  Every step that can fail on one rank alone is followed by a collective
+    agreement (an all-reduce of a success flag), so that all ranks take the same exit path: none is left inside a
+    collective that a failed peer never joins, and none exits while a peer still maps its memory."""
+    import datetime
+    import traceback
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      TORCH_SYMM_MEM_DISABLE_MULTICAST="1")       # plain peer mappings, no NVLink multicast objects
+    joined = False
     try:
-        import torch.distributed as dist
-        import torch.distributed._symmetric_memory as symm
-        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
         torch.cuda.set_device(rank)
         d = torch.device("cuda", rank)
-        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=d)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=d,
+                                timeout=datetime.timedelta(seconds=60))
+        joined = True
+
+        def all_ok(ok):
+            t = torch.tensor([0.0 if ok else 1.0], device=d)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return t.item() == 0.0
+
         M, N, K = 512, 1024, 1024
         A, B, a_s, b_s = h.make_inputs(M, N, K, seed=43)
         n0, nl = plan_n_shards(N, world)[rank]
-        Cfull = symm.empty((M, N), dtype=torch.bfloat16, device=d)
-        Cfull.fill_(float("nan"))
+        err, Cfull, hdl = "", None, None
+        try:
+            import torch.distributed._symmetric_memory as symm
+            Cfull = symm.empty((M, N), dtype=torch.bfloat16, device=d)
+            Cfull.fill_(float("nan"))
+        except Exception:
+            err = traceback.format_exc()[-1500:]
+        if not all_ok(Cfull is not None):                  # before the rendezvous, which is itself collective
+            q.put((rank, -1, err or "symmetric memory unavailable on another rank"))
+            return
         hdl = symm.rendezvous(Cfull, dist.group.WORLD.group_name)
         dist.barrier()
         torch.cuda.synchronize()
-        dA = torch.from_numpy(A).to(d)
-        dB = torch.from_numpy(np.ascontiguousarray(B.reshape(K, N)[:, n0:n0 + nl]).ravel()).to(d)
-        f.gemm_scatter(dA, dB, torch.from_numpy(a_s).to(d), torch.from_numpy(b_s).to(d),
-                       [int(p) for p in hdl.buffer_ptrs], M, nl, K, n0, N)
+        bad = -1
+        try:
+            dA = torch.from_numpy(A).to(d)
+            dB = torch.from_numpy(np.ascontiguousarray(B.reshape(K, N)[:, n0:n0 + nl]).ravel()).to(d)
+            f.gemm_scatter(dA, dB, torch.from_numpy(a_s).to(d), torch.from_numpy(b_s).to(d),
+                           [int(p) for p in hdl.buffer_ptrs], M, nl, K, n0, N)
+            torch.cuda.synchronize()
+            f.last_device_status()
+            bad = 0
+        except Exception:
+            err = traceback.format_exc()[-1500:]
+        wrote = all_ok(bad == 0)                           # doubles as the barrier: every rank's stores have drained
         torch.cuda.synchronize()
-        dist.barrier()                       # every rank has written its columns into every C
-        torch.cuda.synchronize()
-        f.last_device_status()
-        bits = Cfull.view(torch.int16).cpu().numpy().view(np.uint16)
-        bad, first, maxerr = h.mismatches(h.oracle_gemm(A, B, a_s, b_s, M, N, K), bits)
-        q.put((rank, bad, ""))
-        dist.barrier()
-        dist.destroy_process_group()
-    except Exception as exc:          # report instead of hanging the parent
-        import traceback
+        if wrote:
+            bits = Cfull.view(torch.int16).cpu().numpy().view(np.uint16)
+            bad, first, maxerr = h.mismatches(h.oracle_gemm(A, B, a_s, b_s, M, N, K), bits)
+            err = "" if bad == 0 else "first mismatch at %d, max err %g" % (first, maxerr)
+        q.put((rank, bad if wrote else -1, err or "a peer failed"))
+        all_ok(True)                                       # nobody unmaps while a peer is still reading its copy
+        del hdl, Cfull
+    except Exception:                 # report instead of hanging the parent
         q.put((rank, -1, traceback.format_exc()[-1500:]))
+    finally:
+        if joined:
+            try:
+                dist.destroy_process_group()
+            except Exception:
+                pass
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_two_gpus_write_each_others_c():
+    import queue
     import torch.multiprocessing as mp
     world = 2
     ctx = mp.get_context("spawn")
@@ -105,8 +140,20 @@ def test_two_gpus_write_each_others_c():
     procs = [ctx.Process(target=_rank_main, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
-    results = [q.get(timeout=300) for _ in range(world)]
-    for p in procs:
-        p.join(timeout=60)
+    results = []
+    try:
+        for _ in range(world):
+            try:
+                results.append(q.get(timeout=240))
+            except queue.Empty:
+                break
+    finally:
+        for p in procs:                # the children have reported (or timed out): reap them, whatever happened
+            p.join(timeout=90)
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+                p.join(timeout=30)
+    assert len(results) == world, "only %d of %d ranks reported" % (len(results), world)
     for rank, bad, msg in results:
         assert bad == 0, "rank %d: %s %s" % (rank, bad, msg)

@@ -25,6 +25,10 @@ def _inputs(M, N, K, seed):
     return [torch.from_numpy(x).to(dev) for x in (A, B, a_s, b_s)], (A, B, a_s, b_s)
 
 
+def _bits(t):
+    return t.view(torch.int16).cpu().numpy().view(np.uint16)
+
+
 @pytest.mark.parametrize("M,N,K,splits", [(1024, 512, 7168, 4), (1024, 576, 7168, 3), (256, 256, 1024, 0)])
 def test_static_scratch_matches_the_workspace_entry_point(M, N, K, splits):
     dev = torch.device("cuda:0")
@@ -35,23 +39,48 @@ def test_static_scratch_matches_the_workspace_entry_point(M, N, K, splits):
     for call in range(2):                                   # two calls in a row, different data each time
         (dA, dB, dAs, dBs), host = _inputs(M, N, K, seed=40 + call)
         want = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev)
+        same = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev)
         got = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev)
-        rc = lib.fp8bs_gemm_mn_small(dA.data_ptr(), dB.data_ptr(), dAs.data_ptr(), dBs.data_ptr(), want.data_ptr(),
-                                     M, N, K, splits, ws.data_ptr(), ws.numel(), None)
-        assert rc == 0
-        rc = lib.fp8bs_gemm_mn_small_static(dA.data_ptr(), dB.data_ptr(), dAs.data_ptr(), dBs.data_ptr(),
-                                            got.data_ptr(), M, N, K, splits, None)
-        assert rc == 0
+        args = (dA.data_ptr(), dB.data_ptr(), dAs.data_ptr(), dBs.data_ptr())
+        # the existing entry point (it may pick the cluster reduction: another kernel, same split order) ...
+        assert lib.fp8bs_gemm_mn_small(*args, want.data_ptr(), M, N, K, splits, ws.data_ptr(), ws.numel(), None) == 0
+        # ... and the same kernel the static entry point runs, on a caller-owned workspace
+        assert lib.fp8bs_gemm_ex(*args, same.data_ptr(), M, N, K, 0, N, f.PATH_MN_SMALL, splits, f.SPLIT_WORKSPACE,
+                                 ws.data_ptr(), ws.numel(), None) == 0
         torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info(dev)[0]
+        assert lib.fp8bs_gemm_mn_small_static(*args, got.data_ptr(), M, N, K, splits, None) == 0
+        torch.cuda.synchronize()
+        if call == 1:       # the first call on a device may do one-time set-up; the second must not touch the allocator
+            assert torch.cuda.mem_get_info(dev)[0] == free_before
         f.last_device_status()
-        want_bits = want.view(torch.int16).cpu().numpy().view(np.uint16)
-        got_bits = got.view(torch.int16).cpu().numpy().view(np.uint16)
-        bad, first, maxerr = h.mismatches(want_bits, got_bits)       # |d| <= 1e-3 + 2e-2*|ref|, the suite's tolerance
+        got_bits = _bits(got)
+        # same kernel, same summation order: every bit agrees
+        assert np.array_equal(_bits(same), got_bits), "call %d: differs from the workspace split-K kernel" % call
+        bad, first, maxerr = h.mismatches(_bits(want), got_bits)     # |d| <= 1e-3 + 2e-2*|ref|, the suite's tolerance
         assert bad == 0, "call %d: %d mismatches, first %d, max err %g" % (call, bad, first, maxerr)
         # and both agree with the CPU checker
         rows = np.arange(0, M, 8, dtype=np.int32)
         bad, first, maxerr = h.mismatches(h.oracle_gemm(*host, M, N, K, rows=rows), got_bits[rows])
         assert bad == 0, "call %d vs checker: %d mismatches" % (call, bad)
+
+
+def test_static_scratch_is_usable_after_a_reported_timeout():
+    """The wait-timeout self-test leaves a status behind; once it has been read, the built-in scratch works as before."""
+    dev = torch.device("cuda:0")
+    lib = f.lib()
+    M, N, K, splits = 256, 256, 1024, 4
+    (dA, dB, dAs, dBs), host = _inputs(M, N, K, seed=47)
+    assert lib.fp8bs_selftest_wait_timeout(None) == 0
+    with pytest.raises(f.Fp8bsError):
+        f.last_device_status()
+    got = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev)
+    assert lib.fp8bs_gemm_mn_small_static(dA.data_ptr(), dB.data_ptr(), dAs.data_ptr(), dBs.data_ptr(), got.data_ptr(),
+                                          M, N, K, splits, None) == 0
+    torch.cuda.synchronize()
+    f.last_device_status()
+    bad, first, maxerr = h.mismatches(h.oracle_gemm(*host, M, N, K), _bits(got))
+    assert bad == 0
 
 
 def test_static_scratch_refuses_what_does_not_fit():
