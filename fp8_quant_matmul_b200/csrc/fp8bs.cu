@@ -97,7 +97,7 @@ template <int BN, int CG, int MODE>
 static int prepare_kernel()
 {
     CUDA_TRY(cudaFuncSetAttribute(gemm_kernel<BN, CG, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  TileCfg<BN, CG, MODE>::SMEM_BYTES));
+                                  TileCfg<BN, CG>::SMEM_BYTES));
     return FP8BS_OK;
 }
 
@@ -153,8 +153,8 @@ static int device_setup(DeviceInfo** out)
         for (int cs = 1; cs <= 8; ++cs) {
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3(static_cast<unsigned>(cs * 64), 1, 1);
-            cfg.blockDim = dim3(TileCfg<128, 1, 2>::THREADS, 1, 1);
-            cfg.dynamicSmemBytes = TileCfg<128, 1, 2>::SMEM_BYTES;
+            cfg.blockDim = dim3(TileCfg<128, 1>::THREADS, 1, 1);
+            cfg.dynamicSmemBytes = TileCfg<128, 1>::SMEM_BYTES;
             cudaLaunchAttribute attr[1];
             attr[0].id = cudaLaunchAttributeClusterDimension;
             attr[0].val.clusterDim.x = static_cast<unsigned>(cs);
@@ -415,7 +415,7 @@ struct TensorMaps {
 template <int BN, int CG, int MODE>
 static int launch(const TensorMaps& tm, const GemmParams& p, int sm_count, cudaStream_t stream)
 {
-    using Cfg = TileCfg<BN, CG, MODE>;
+    using Cfg = TileCfg<BN, CG>;
     const int units = p.m_tiles * p.n_tiles * p.splits;
     int groups = units < sm_count / CG ? units : sm_count / CG;    // tile walkers: CTAs or CTA pairs
     if (MODE == 2) groups = units;                                  // one CTA per (tile, K range); a cluster per tile

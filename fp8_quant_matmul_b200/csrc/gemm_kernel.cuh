@@ -101,7 +101,7 @@ struct GemmParams {
 // otherwise unchanged: a per-block hand-off cost ~160 cycles per K block of a loop that has ~512 to spend.
 constexpr int SCALE_GROUP = 8;
 
-template <int BN, int CG, int MODE = 0>
+template <int BN, int CG>
 struct TileCfg {
     static_assert(BN == 128 || BN == 256, "tile width");
     static_assert(CG == 1 || (CG == 2 && BN == 256), "pair tiles are 256 x 256");
@@ -123,9 +123,7 @@ struct TileCfg {
     // a thread's 128 columns), so the second half need not wait for the first store to drain; pair tiles, used for long
     // K where the epilogue is a small part, keep one box and the extra pipeline stage instead.
     static constexpr int NSTG = (CG == 1) ? COLS / 64 : 1;
-    // MODE 2 (cluster split-K) writes C with plain stores after the reduction: no staging boxes, so the shared memory
-    // buys one more pipeline stage, which these load-latency-bound configurations need most
-    static constexpr int STG_BYTES = (MODE == 2) ? 0 : PROMO_WARPS * 4096 * NSTG;
+    static constexpr int STG_BYTES = PROMO_WARPS * 4096 * NSTG;
     static constexpr int SGRP = SCALE_GROUP;          // K blocks per a_scale ring entry (one TMA box {128 rows, SGRP})
     static constexpr int SRING = 4;                   // a_scale ring entries
     static constexpr int SRING_BYTES = SRING * SGRP * 512;
@@ -150,7 +148,8 @@ constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;  // about one second
 //                               CTA's lifetime in cycles
 //   [4096 + event * 128 + kb]   level 3, CTA 0, first 128 K blocks, clock64 at: 0 TMEM buffer free (MMA warp),
 //                               1 operands there, 2 MMAs and commits issued, 3 a_scale there (promotion warp 4),
-//                               4 partial sums there, 5 FMAs done, 6 stage free (producer), 7 / 8 = 4 / 5 for warp 5
+//                               4 partial sums there, 5 FMAs done, 6 stage free (producer), 7 / 8 = 4 / 5 for warp 5;
+//                               [4096 + (9 or 10) * 128 + unit]: start / end of the epilogue of CTA 0's unit
 #ifdef FP8BS_PROFILE
 #define PROF_DECL(name) long long name = 0
 #if FP8BS_PROFILE >= 2 && !defined(FP8BS_PROFILE_NOTIMERS)   // per-wait timers: they perturb the loops they measure
@@ -278,51 +277,12 @@ __global__ void wait_timeout_selftest_kernel(unsigned int* status, long long lim
     (void)ok;
 }
 
-// Cluster split-K, final step: this CTA finishes rows [r0, r1) of the tile.  Every element is the sum of the S partial
-// tiles in the order 0, 1, .., S-1 (bit-deterministic), read out of the S CTAs' shared memory (peer[s] = cluster
-// address of CTA s's partial tile, rows of `pitch` bytes).  A remote shared-memory load takes several hundred cycles,
-// so the loads of UNR items (UNR * S of them) are issued before the first sum.
-template <int BN, int S, int UNR>
-__device__ __forceinline__ void cluster_reduce_store(const uint32_t (&peer)[8], int r0, int r1, int tid, int nthreads,
-                                                     int pitch, __nv_bfloat16* C, int m0, int n0, int M, int N)
-{
-    const int items = (r1 - r0) * (BN / 4);
-    for (int base = tid; base < items; base += nthreads * UNR) {
-        float4 v[UNR][S];
-#pragma unroll
-        for (int j = 0; j < UNR; ++j) {
-            const int idx = base + j * nthreads;
-            if (idx < items) {
-                const uint32_t off = static_cast<uint32_t>((r0 + idx / (BN / 4)) * pitch + (idx % (BN / 4)) * 16);
-#pragma unroll
-                for (int s = 0; s < S; ++s) v[j][s] = ptx::ld_shared_cluster_v4(peer[s] + off);
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < UNR; ++j) {
-            const int idx = base + j * nthreads;
-            if (idx < items) {
-                float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-#pragma unroll
-                for (int s = 0; s < S; ++s) { sum.x += v[j][s].x; sum.y += v[j][s].y; sum.z += v[j][s].z; sum.w += v[j][s].w; }
-                const int m = m0 + r0 + idx / (BN / 4), n = n0 + (idx % (BN / 4)) * 4;
-                if (m < M && n < N) {
-                    uint2 q;
-                    q.x = pack_bf16x2(sum.x, sum.y);
-                    q.y = pack_bf16x2(sum.z, sum.w);
-                    *reinterpret_cast<uint2*>(C + static_cast<size_t>(m) * N + n) = q;
-                }
-            }
-        }
-    }
-}
-
 template <int BN, int CG, int MODE>
-__global__ void __launch_bounds__(TileCfg<BN, CG, MODE>::THREADS, 1)
+__global__ void __launch_bounds__(TileCfg<BN, CG>::THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmAs, const __grid_constant__ CMaps cmaps, const GemmParams p)
 {
-    using Cfg = TileCfg<BN, CG, MODE>;
+    using Cfg = TileCfg<BN, CG>;
     constexpr int STAGES = Cfg::STAGES;
     constexpr int NBUF = Cfg::NBUF;
     constexpr int SRING = Cfg::SRING;
@@ -489,11 +449,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 const long long t0 = clock64();
                 while (clock64() - t0 < 2000000LL) __nanosleep(1000);
             }
-        } else if ((warp == 1 || (CG == 1 && warp == 3)) && lane == 0 && rank == 0) {
+        } else if (warp == 1 && lane == 0 && rank == 0) {
             // ---------------------------------------------------- MMA issuer ----------------
             constexpr uint32_t idesc = ptx::make_idesc_e4m3_mnmajor(Cfg::TILE_M, BN);
-            constexpr uint32_t n_issuers = (CG == 1) ? 2u : 1u;
-            const uint32_t my_issuer = (warp == 1) ? 0u : 1u;
             uint32_t it = 0, ait = 0;
             bool ok = true;
             PROF_DECL(w_tempty); PROF_DECL(w_full); PROF_DECL(t_mma_total);
@@ -506,7 +464,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 int tile, m0, n0, kb0, kb1;
                 decode(u, tile, m0, n0, kb0, kb1);
                 for (int kb = kb0; kb < kb1; ++kb, ++it, ++ait) {
-                    if (n_issuers > 1 && (it % n_issuers) != my_issuer) continue;
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1u;
                     const int b = ait % NBUF;
@@ -574,10 +531,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             }
         }
         __syncwarp();
-        if constexpr (MODE == 2) {           // the barriers around the cluster reduction (done by the promotion warps)
-            __syncthreads();
-            ptx::cluster_sync();
-        }
     } else {
         // -------------------------------------------------------- promotion + epilogue ------
         ptx::setmaxnreg_inc<216>();
@@ -633,7 +586,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             // b_scale is tiny and warp-uniform.  Lane l holds the values of K block (base + l); every 32 blocks
             // the vector loaded one round earlier takes over, so no iteration waits on a global load.  The first two
             // vectors of a unit were fetched before the previous unit's epilogue (pf_*), so a tile switch does not
-            // wait on global memory either: with two K blocks per tile that wait was a quarter of the tile's time.
+            // wait on global memory either (measured: 3 % on 1024 x 7168 x 256, neutral elsewhere).
             const float* bl_ptr = p.b_scale + nb_lo;
             const float* bh_ptr = p.b_scale + nb_hi;
             auto load_bvec = [&](const float* ptr, int kbase) {
@@ -696,8 +649,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                             else ptx::mbar_arrive(tempty_bar(b));
                         }
                     }
-                    ptx::fma32_from64_0(acc[2 * q], v, (2 * q >= hi_from) ? s_hi2 : s_lo2);
-                    ptx::fma32_from64_32(acc[2 * q + 1], v, (2 * q + 1 >= hi_from) ? s_hi2 : s_lo2);
+                    ptx::fma32_from64<0>(acc[2 * q], v, (2 * q >= hi_from) ? s_hi2 : s_lo2);
+                    ptx::fma32_from64<32>(acc[2 * q + 1], v, (2 * q + 1 >= hi_from) ? s_hi2 : s_lo2);
                 }
                 // Release the a_scale ring entry after its last K block, and only after the FMAs that consumed the
                 // value.  An arrive placed straight after the shared-memory read of a_scale (its value not yet
@@ -895,31 +848,39 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         // C must have been read out of shared memory before the CTA goes away
         if (lane == 0) ptx::tma_store_wait_read<0>();
         __syncwarp();
-        if constexpr (MODE == 2) {
-            // -------------------------------------------------------- cluster reduction ---
-            // (inside this branch: the code after the role branches is compiled for the small register budget of
-            // warps 0-3, and the reduction keeps dozens of remote loads in flight)
-            __syncthreads();                 // this CTA's partial tile is complete ...
-            ptx::cluster_sync();             // ... and so are those of the other K ranges of the tile
-            if (*abort_flag == 0u) {
-                const int S = p.splits;
-                const int my = static_cast<int>(ptx::cluster_ctarank());     // = this CTA's split index
-                int tile, m0, n0, kb0, kb1;
-                decode(static_cast<int>(blockIdx.x), tile, m0, n0, kb0, kb1);
-                const int r0 = (128 * my) / S, r1 = (128 * (my + 1)) / S;     // the rows this CTA finishes
-                uint32_t peer[8];
+    }
+
+    if constexpr (MODE == 2) {
+        // ------------------------------------------------------------ cluster reduction ---
+        __syncthreads();                 // this CTA's partial tile is complete ...
+        ptx::cluster_sync();             // ... and so are those of the other K ranges of the tile
+        if (warp >= 4 && *abort_flag == 0u) {
+            const int S = p.splits;
+            const int my = static_cast<int>(ptx::cluster_ctarank());     // = this CTA's split index
+            int tile, m0, n0, kb0, kb1;
+            decode(static_cast<int>(blockIdx.x), tile, m0, n0, kb0, kb1);
+            const int r0 = (128 * my) / S, r1 = (128 * (my + 1)) / S;     // the rows this CTA finishes
+            uint32_t peer[8];
 #pragma unroll
-                for (int s = 0; s < 8; ++s) peer[s] = ptx::mapa(stage_base, static_cast<uint32_t>(s < S ? s : 0));
-                const int tid = static_cast<int>(threadIdx.x) - 128;
-                switch (S) {
-                    case 1: cluster_reduce_store<BN, 1, 4>(peer, r0, r1, tid, Cfg::PROMO_THREADS, PART_PITCH, p.C, m0, n0, p.M, p.N); break;
-                    case 2: cluster_reduce_store<BN, 2, 4>(peer, r0, r1, tid, Cfg::PROMO_THREADS, PART_PITCH, p.C, m0, n0, p.M, p.N); break;
-                    case 3: cluster_reduce_store<BN, 3, 4>(peer, r0, r1, tid, Cfg::PROMO_THREADS, PART_PITCH, p.C, m0, n0, p.M, p.N); break;
-                    case 4: cluster_reduce_store<BN, 4, 4>(peer, r0, r1, tid, Cfg::PROMO_THREADS, PART_PITCH, p.C, m0, n0, p.M, p.N); break;
-                    case 5: cluster_reduce_store<BN, 5, 2>(peer, r0, r1, tid, Cfg::PROMO_THREADS, PART_PITCH, p.C, m0, n0, p.M, p.N); break;
-                    case 6: cluster_reduce_store<BN, 6, 2>(peer, r0, r1, tid, Cfg::PROMO_THREADS, PART_PITCH, p.C, m0, n0, p.M, p.N); break;
-                    case 7: cluster_reduce_store<BN, 7, 2>(peer, r0, r1, tid, Cfg::PROMO_THREADS, PART_PITCH, p.C, m0, n0, p.M, p.N); break;
-                    default: cluster_reduce_store<BN, 8, 2>(peer, r0, r1, tid, Cfg::PROMO_THREADS, PART_PITCH, p.C, m0, n0, p.M, p.N); break;
+            for (int s = 0; s < 8; ++s) peer[s] = ptx::mapa(stage_base, static_cast<uint32_t>(s < S ? s : 0));
+            const int items = (r1 - r0) * (BN / 4);
+            for (int idx = static_cast<int>(threadIdx.x) - 128; idx < items; idx += Cfg::PROMO_THREADS) {
+                const int row = r0 + idx / (BN / 4), c4 = idx % (BN / 4);
+                const uint32_t off = static_cast<uint32_t>(row * PART_PITCH + c4 * 16);
+                float4 v[8];
+#pragma unroll
+                for (int s = 0; s < 8; ++s)
+                    if (s < S) v[s] = ptx::ld_shared_cluster_v4(peer[s] + off);
+                float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+                for (int s = 0; s < 8; ++s)              // fixed order 0, 1, .., S-1: bit-deterministic
+                    if (s < S) { sum.x += v[s].x; sum.y += v[s].y; sum.z += v[s].z; sum.w += v[s].w; }
+                const int m = m0 + row, n = n0 + c4 * 4;
+                if (m < p.M && n < p.N) {
+                    uint2 q;
+                    q.x = pack_bf16x2(sum.x, sum.y);
+                    q.y = pack_bf16x2(sum.z, sum.w);
+                    *reinterpret_cast<uint2*>(p.C + static_cast<size_t>(m) * p.N + n) = q;
                 }
             }
         }

@@ -248,8 +248,9 @@ __device__ __forceinline__ void setmaxnreg_dec()
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
 // ---------------------------------------------------------------- promotion ---------
-// acc[0..15] += sc * cur[0..31] (two columns per instruction), cur being a 64-column buffer.
-__device__ __forceinline__ void fma32_from64_0(unsigned long long (&acc)[16], const uint32_t (&cur)[64], unsigned long long sc2)
+// acc[0..15] += sc * cur[OFF .. OFF+31] (two columns per instruction), cur being a 64-column buffer.
+template <int OFF>
+__device__ __forceinline__ void fma32_from64(unsigned long long (&acc)[16], const uint32_t (&cur)[64], unsigned long long sc2)
 {
     asm volatile(
         "{\n\t.reg .b64 t;\n\t"
@@ -271,33 +272,7 @@ __device__ __forceinline__ void fma32_from64_0(unsigned long long (&acc)[16], co
         "mov.b64 t, {%46, %47};\n\tfma.rn.f32x2 %15, t, %48, %15;\n\t"
         "}"
         : "+l"(acc[0]), "+l"(acc[1]), "+l"(acc[2]), "+l"(acc[3]), "+l"(acc[4]), "+l"(acc[5]), "+l"(acc[6]), "+l"(acc[7]), "+l"(acc[8]), "+l"(acc[9]), "+l"(acc[10]), "+l"(acc[11]), "+l"(acc[12]), "+l"(acc[13]), "+l"(acc[14]), "+l"(acc[15])
-        : "r"(cur[0]), "r"(cur[1]), "r"(cur[2]), "r"(cur[3]), "r"(cur[4]), "r"(cur[5]), "r"(cur[6]), "r"(cur[7]), "r"(cur[8]), "r"(cur[9]), "r"(cur[10]), "r"(cur[11]), "r"(cur[12]), "r"(cur[13]), "r"(cur[14]), "r"(cur[15]), "r"(cur[16]), "r"(cur[17]), "r"(cur[18]), "r"(cur[19]), "r"(cur[20]), "r"(cur[21]), "r"(cur[22]), "r"(cur[23]), "r"(cur[24]), "r"(cur[25]), "r"(cur[26]), "r"(cur[27]), "r"(cur[28]), "r"(cur[29]), "r"(cur[30]), "r"(cur[31]), "l"(sc2));
-}
-
-// acc[0..15] += sc * cur[32..63] (two columns per instruction), cur being a 64-column buffer.
-__device__ __forceinline__ void fma32_from64_32(unsigned long long (&acc)[16], const uint32_t (&cur)[64], unsigned long long sc2)
-{
-    asm volatile(
-        "{\n\t.reg .b64 t;\n\t"
-        "mov.b64 t, {%16, %17};\n\tfma.rn.f32x2 %0, t, %48, %0;\n\t"
-        "mov.b64 t, {%18, %19};\n\tfma.rn.f32x2 %1, t, %48, %1;\n\t"
-        "mov.b64 t, {%20, %21};\n\tfma.rn.f32x2 %2, t, %48, %2;\n\t"
-        "mov.b64 t, {%22, %23};\n\tfma.rn.f32x2 %3, t, %48, %3;\n\t"
-        "mov.b64 t, {%24, %25};\n\tfma.rn.f32x2 %4, t, %48, %4;\n\t"
-        "mov.b64 t, {%26, %27};\n\tfma.rn.f32x2 %5, t, %48, %5;\n\t"
-        "mov.b64 t, {%28, %29};\n\tfma.rn.f32x2 %6, t, %48, %6;\n\t"
-        "mov.b64 t, {%30, %31};\n\tfma.rn.f32x2 %7, t, %48, %7;\n\t"
-        "mov.b64 t, {%32, %33};\n\tfma.rn.f32x2 %8, t, %48, %8;\n\t"
-        "mov.b64 t, {%34, %35};\n\tfma.rn.f32x2 %9, t, %48, %9;\n\t"
-        "mov.b64 t, {%36, %37};\n\tfma.rn.f32x2 %10, t, %48, %10;\n\t"
-        "mov.b64 t, {%38, %39};\n\tfma.rn.f32x2 %11, t, %48, %11;\n\t"
-        "mov.b64 t, {%40, %41};\n\tfma.rn.f32x2 %12, t, %48, %12;\n\t"
-        "mov.b64 t, {%42, %43};\n\tfma.rn.f32x2 %13, t, %48, %13;\n\t"
-        "mov.b64 t, {%44, %45};\n\tfma.rn.f32x2 %14, t, %48, %14;\n\t"
-        "mov.b64 t, {%46, %47};\n\tfma.rn.f32x2 %15, t, %48, %15;\n\t"
-        "}"
-        : "+l"(acc[0]), "+l"(acc[1]), "+l"(acc[2]), "+l"(acc[3]), "+l"(acc[4]), "+l"(acc[5]), "+l"(acc[6]), "+l"(acc[7]), "+l"(acc[8]), "+l"(acc[9]), "+l"(acc[10]), "+l"(acc[11]), "+l"(acc[12]), "+l"(acc[13]), "+l"(acc[14]), "+l"(acc[15])
-        : "r"(cur[32]), "r"(cur[33]), "r"(cur[34]), "r"(cur[35]), "r"(cur[36]), "r"(cur[37]), "r"(cur[38]), "r"(cur[39]), "r"(cur[40]), "r"(cur[41]), "r"(cur[42]), "r"(cur[43]), "r"(cur[44]), "r"(cur[45]), "r"(cur[46]), "r"(cur[47]), "r"(cur[48]), "r"(cur[49]), "r"(cur[50]), "r"(cur[51]), "r"(cur[52]), "r"(cur[53]), "r"(cur[54]), "r"(cur[55]), "r"(cur[56]), "r"(cur[57]), "r"(cur[58]), "r"(cur[59]), "r"(cur[60]), "r"(cur[61]), "r"(cur[62]), "r"(cur[63]), "l"(sc2));
+        : "r"(cur[OFF + 0]), "r"(cur[OFF + 1]), "r"(cur[OFF + 2]), "r"(cur[OFF + 3]), "r"(cur[OFF + 4]), "r"(cur[OFF + 5]), "r"(cur[OFF + 6]), "r"(cur[OFF + 7]), "r"(cur[OFF + 8]), "r"(cur[OFF + 9]), "r"(cur[OFF + 10]), "r"(cur[OFF + 11]), "r"(cur[OFF + 12]), "r"(cur[OFF + 13]), "r"(cur[OFF + 14]), "r"(cur[OFF + 15]), "r"(cur[OFF + 16]), "r"(cur[OFF + 17]), "r"(cur[OFF + 18]), "r"(cur[OFF + 19]), "r"(cur[OFF + 20]), "r"(cur[OFF + 21]), "r"(cur[OFF + 22]), "r"(cur[OFF + 23]), "r"(cur[OFF + 24]), "r"(cur[OFF + 25]), "r"(cur[OFF + 26]), "r"(cur[OFF + 27]), "r"(cur[OFF + 28]), "r"(cur[OFF + 29]), "r"(cur[OFF + 30]), "r"(cur[OFF + 31]), "l"(sc2));
 }
 
 // 64 columns from TMEM, complete on return (load and wait in one statement).
