@@ -374,7 +374,10 @@ def format_kernels_bench(torch, f, dev, hbm_gbs):
                              "GBps": round(by / us / 1e3, 1), "frac_of_hbm_peak": round(by / us / 1e3 / hbm_gbs, 3)}
     del xs, ws
     n = M * K                                                                            # 44 MB, as A of the big shape
-    srcs = [torch.randint(8, 0x78, (n,), dtype=torch.uint8, device=dev) for _ in range(7)]  # 7 x 44 MB > 2 x L2
+    # reference-format (e4m3fnuz) bytes of the benchmark's element distribution: fn byte + 8, zero stays zero
+    fn = torch.from_numpy(f.gen_normal_e4m3(n, 4242)).to(dev)
+    fnuz = torch.where((fn & 0x7F) == 0, torch.zeros_like(fn), fn + 8)
+    srcs = [torch.roll(fnuz, 4099 * i) if i else fnuz for i in range(7)]                    # 7 x 44 MB > 2 x L2
     dst = torch.empty(n, dtype=torch.uint8, device=dev)
 
     def conv():

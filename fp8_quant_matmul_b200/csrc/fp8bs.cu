@@ -1098,23 +1098,39 @@ __device__ __forceinline__ uint32_t fnuz_to_fn_byte(uint32_t b, unsigned int& in
     return sign | h;                                    // h <= 8; 8 is the encoding of 2^-6
 }
 
-__global__ void fnuz_to_fn_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, size_t n16,
-                                  const uint8_t* __restrict__ src_tail, uint8_t* __restrict__ dst_tail, int tail,
-                                  unsigned int* __restrict__ inexact_count)
+// Four bytes at a time.  A byte whose low seven bits are >= 0x10 (exponent field >= 2) is a normal number of both
+// dialects and only loses 8; a word of four such bytes -- nearly every word of real data -- is one subtraction.
+__device__ __forceinline__ uint32_t fnuz_to_fn_word(uint32_t w, unsigned int& inexact)
+{
+    const uint32_t low7 = w & 0x7F7F7F7Fu;
+    // per byte: bit 7 set iff low7 >= 0x10  (adding 0x70 carries into bit 7 exactly then; no carry crosses bytes)
+    if (((low7 + 0x70707070u) & 0x80808080u) == 0x80808080u) return w - 0x08080808u;
+    uint32_t o = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o |= fnuz_to_fn_byte((w >> (8 * j)) & 0xFFu, inexact) << (8 * j);
+    return o;
+}
+
+__global__ void __launch_bounds__(256)
+fnuz_to_fn_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, size_t n16,
+                  const uint8_t* __restrict__ src_tail, uint8_t* __restrict__ dst_tail, int tail,
+                  unsigned int* __restrict__ inexact_count)
 {
     unsigned int inexact = 0;
-    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n16;
-         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-        uint4 v = src[i];
-        uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            uint32_t o = 0;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) o |= fnuz_to_fn_byte((w[k] >> (8 * j)) & 0xFFu, inexact) << (8 * j);
-            w[k] = o;
-        }
-        dst[i] = make_uint4(w[0], w[1], w[2], w[3]);
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    // two independent 16-byte loads in flight per thread and round
+    for (; i + stride < n16; i += 2 * stride) {
+        const uint4 a = __ldcs(src + i), b = __ldcs(src + i + stride);
+        dst[i] = make_uint4(fnuz_to_fn_word(a.x, inexact), fnuz_to_fn_word(a.y, inexact), fnuz_to_fn_word(a.z, inexact),
+                            fnuz_to_fn_word(a.w, inexact));
+        dst[i + stride] = make_uint4(fnuz_to_fn_word(b.x, inexact), fnuz_to_fn_word(b.y, inexact),
+                                     fnuz_to_fn_word(b.z, inexact), fnuz_to_fn_word(b.w, inexact));
+    }
+    if (i < n16) {
+        const uint4 a = __ldcs(src + i);
+        dst[i] = make_uint4(fnuz_to_fn_word(a.x, inexact), fnuz_to_fn_word(a.y, inexact), fnuz_to_fn_word(a.z, inexact),
+                            fnuz_to_fn_word(a.w, inexact));
     }
     if (blockIdx.x == 0 && static_cast<int>(threadIdx.x) < tail)
         dst_tail[threadIdx.x] = static_cast<uint8_t>(fnuz_to_fn_byte(src_tail[threadIdx.x], inexact));
@@ -1133,7 +1149,7 @@ int fp8bs_fnuz_to_fn_device(void* dst, const void* src, size_t n, unsigned int* 
     const size_t n16 = n / 16;
     const int tail = static_cast<int>(n % 16);
     size_t blocks = (n16 + 255) / 256;
-    const size_t cap = static_cast<size_t>(dev->sm_count) * 8;
+    const size_t cap = static_cast<size_t>(dev->sm_count) * 8;      // 8 resident CTAs of 256 threads per SM
     if (blocks > cap) blocks = cap;
     if (blocks == 0) blocks = 1;
     fnuz_to_fn_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(

@@ -9,8 +9,13 @@
 // (out[r + rows*k], the layout of mn_large.hip:13-14) and the inverse scales go to scale_out[r + rows*kb] (row-wise)
 // or scale_out[rb + ceil(rows/128)*kb] (block) -- exactly what the GEMM reads (check.cu:42-46).
 //
-// One CTA handles a 128 x 128 tile: 64 KB read with float4 loads, each thread keeps its 64 values in registers,
-// the fp8 bytes are transposed through shared memory so that global writes are 128-byte runs along the rows index.
+// One CTA handles a 128 x 128 tile: 64 KB read with float4 loads, each thread keeps its 64 values in registers.  The
+// fp8 bytes go through shared memory as 32-bit words that hold four consecutive rows at one k -- four bytes that are
+// also neighbours in the column-major output -- laid out [row group][k] with a pitch of 132 words: a thread writes its
+// four k of a row group as one 16-byte store (a warp: 512 contiguous bytes), and reads back 16 bytes with lane = row
+// group, which is conflict-free per quarter warp; each word then leaves in a 128-byte coalesced run along the rows.
+// The conversion is the hardware's cvt.rn.satfinite.e4m3x2.f32 (round to nearest even; the clamp before it keeps
+// every value inside the format's range, where it equals torch's cast bit for bit).
 #pragma once
 #include <cuda_bf16.h>
 #include <cstdint>
@@ -18,6 +23,14 @@
 namespace fp8bs {
 
 __host__ __device__ inline uint8_t float_to_e4m3fn_rne(float x);   // defined in fp8bs.cu
+
+// Two fp32 -> two e4m3fn bytes (lo in bits 0-7, hi in bits 8-15), round to nearest even.
+__device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi)
+{
+    uint16_t r;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+    return r;
+}
 
 template <bool BLOCK_SCALE, typename InT>
 __global__ void __launch_bounds__(256)
@@ -27,7 +40,8 @@ quantize_kernel(const InT* __restrict__ X, uint8_t* __restrict__ out, float* __r
     // tile: rows [r0, r0+128), k [k0, k0+128)
     const int r0 = blockIdx.x * 128, kb = blockIdx.y, k0 = kb * 128;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    __shared__ __align__(16) uint8_t tile[128][144];   // [k][row], pitch 144 = 128 + 16: 16-byte aligned rows, fewer conflicts
+    constexpr int PITCH = 132;                                   // words per row group: 128 k + 4 (16-byte aligned rows)
+    __shared__ __align__(16) uint32_t tile[32 * PITCH];          // [row group of 4][k]: one word = 4 rows at one k
     __shared__ float warp_max[8];
 
     // each warp owns 16 rows; lane holds 4 consecutive k of every one of them
@@ -40,9 +54,9 @@ quantize_kernel(const InT* __restrict__ X, uint8_t* __restrict__ out, float* __r
         if (r < rows) {
             const InT* src = X + static_cast<size_t>(r) * K + k0 + lane * 4;
             if constexpr (sizeof(InT) == 4) {
-                x = *reinterpret_cast<const float4*>(src);
+                x = __ldcs(reinterpret_cast<const float4*>(src));            // streamed: read once
             } else {
-                const uint2 raw = *reinterpret_cast<const uint2*>(src);
+                const uint2 raw = __ldcs(reinterpret_cast<const uint2*>(src));
                 const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
                 const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
                 x = make_float4(__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi));
@@ -66,32 +80,53 @@ quantize_kernel(const InT* __restrict__ X, uint8_t* __restrict__ out, float* __r
 #pragma unroll
         for (int i = 0; i < 16; ++i) amax[i] = m;      // one scale for the whole 128 x 128 block
     }
+    float scale[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
         const float a = fmaxf(amax[i], 1e-12f);                       // .clamp(min=1e-12)   quantize.py:29, 57
         // finfo.max / absmax (quantize.py:30, 58): for a tensor divisor torch evaluates this as reciprocal(absmax) * max
-        const float scale = __fmul_rn(__fdiv_rn(1.0f, a), fp8_max);
-        const int rl = warp * 16 + i;
+        scale[i] = __fmul_rn(__fdiv_rn(1.0f, a), fp8_max);
+    }
+    if constexpr (!BLOCK_SCALE) {
+        // lane i stores the inverse scale of the warp's row i: one 64-byte run per warp
+        float mine = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+            if (lane == i) mine = __fdiv_rn(1.0f, scale[i]);                                   // reciprocal, quantize.py:65
+        const int rl = warp * 16 + lane;
+        if (lane < 16 && r0 + rl < rows) scale_out[static_cast<size_t>(kb) * rows + r0 + rl] = mine;
+    }
+    if (BLOCK_SCALE && threadIdx.x == 0)
+        scale_out[static_cast<size_t>(kb) * gridDim.x + blockIdx.x] = __fdiv_rn(1.0f, scale[0]);
+    // quantise; rows 4g .. 4g+3 of this warp at k = 4*lane + j become one word
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        uint32_t w[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            float q = __fmul_rn(v[i][j], scale);
-            q = fminf(fmaxf(q, -fp8_max), fp8_max);                   // .clamp(min, max)    quantize.py:33, 61
-            tile[lane * 4 + j][rl] = float_to_e4m3fn_rne(q);
+            float q[4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                const float x = __fmul_rn(v[4 * g + t][j], scale[4 * g + t]);
+                q[t] = fminf(fmaxf(x, -fp8_max), fp8_max);             // .clamp(min, max)    quantize.py:33, 61
+            }
+            w[j] = cvt_e4m3x2(q[0], q[1]) | (cvt_e4m3x2(q[2], q[3]) << 16);
         }
-        if (!BLOCK_SCALE && lane == 0 && r0 + rl < rows)
-            scale_out[static_cast<size_t>(kb) * rows + r0 + rl] = __fdiv_rn(1.0f, scale);      // reciprocal, quantize.py:65
-    }
-    if (BLOCK_SCALE && threadIdx.x == 0) {
-        const float a = fmaxf(amax[0], 1e-12f);
-        scale_out[static_cast<size_t>(kb) * gridDim.x + blockIdx.x] = __fdiv_rn(1.0f, __fmul_rn(__fdiv_rn(1.0f, a), fp8_max));
+        *reinterpret_cast<uint4*>(&tile[(warp * 4 + g) * PITCH + lane * 4]) = make_uint4(w[0], w[1], w[2], w[3]);
     }
     __syncthreads();
-    // write out: k-row by k-row, 128 bytes (128 rows of the input) at a time; a thread moves 16 bytes
-    for (int idx = threadIdx.x; idx < 128 * 8; idx += 256) {
-        const int k = idx >> 3, c = (idx & 7) * 16;
-        if (r0 + c < rows) {       // rows % 16 == 0 is required by the GEMM, so a 16-byte run is all in or all out
-            const uint4 q = *reinterpret_cast<const uint4*>(&tile[k][c]);
-            *reinterpret_cast<uint4*>(out + static_cast<size_t>(k0 + k) * rows + r0 + c) = q;
+    // write out: lane = row group, a warp instruction stores 128 consecutive bytes of one k-row of the output
+    // (rows % 16 == 0 is required by the GEMM, so a 4-row word is all in or all out)
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+        const int kq = (warp + 8 * it) * 4;                            // this warp's four k in this round
+        const uint4 q = *reinterpret_cast<const uint4*>(&tile[lane * PITCH + kq]);
+        if (r0 + lane * 4 < rows) {
+            uint8_t* dst = out + static_cast<size_t>(k0 + kq) * rows + r0 + lane * 4;
+            *reinterpret_cast<uint32_t*>(dst) = q.x;
+            *reinterpret_cast<uint32_t*>(dst + rows) = q.y;
+            *reinterpret_cast<uint32_t*>(dst + 2 * static_cast<size_t>(rows)) = q.z;
+            *reinterpret_cast<uint32_t*>(dst + 3 * static_cast<size_t>(rows)) = q.w;
         }
     }
 }

@@ -156,7 +156,7 @@ int fp8bs_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
 int fp8bs_last_device_status(void* stream, unsigned int* detail);
 
 /* Failure-path self-test (no counterpart in the reference, which has no error handling): launches one warp that
- * waits, with a limit of about 20 ms, on a barrier nothing arrives on.  The wait gives up, the kernel ends normally,
+ * waits, with a limit of 40 M cycles (about 20 ms), on a barrier nothing arrives on.  The wait gives up, the kernel ends normally,
  * and the next fp8bs_last_device_status returns FP8BS_ERR_DEVICE_TIMEOUT (detail & 0xFF == 9); the context stays usable. */
 int fp8bs_selftest_wait_timeout(void* stream);
 

@@ -89,3 +89,50 @@ def test_world_size_2_gloo_partition_and_gather():
         p.join(timeout=60)
         assert p.exitcode == 0
     assert sorted(results) == [(0, True), (1, True)]
+
+
+def _leaving_worker(rank, world, port, q):
+    """Three steps; rank 1 leaves after the first one (between steps, nothing of its in flight).  The others learn of
+    it on the host: their next collective ends with an error after the short process-group timeout."""
+    import datetime
+    import time
+    import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    steps_done, noticed = 0, None
+    try:
+        for step in range(3):
+            t = torch.tensor([float(rank)])
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)             # stands for the step's barrier / max-over-ranks
+            steps_done += 1
+            if rank == 1 and step == 0:
+                q.put((rank, steps_done, "left"))
+                return                                           # leaves without calling any further collective
+            time.sleep(0.1)
+    except Exception as e:                                       # the survivor's next collective fails: detected
+        noticed = type(e).__name__
+    q.put((rank, steps_done, noticed))
+
+
+def test_a_rank_that_leaves_between_steps_is_noticed_by_the_others():
+    torch = pytest.importorskip("torch")
+    import torch.multiprocessing as mp
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_leaving_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = sorted(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+        if p.is_alive():
+            p.terminate()
+    assert results[1] == (1, 1, "left")
+    rank, steps_done, noticed = results[0]
+    assert rank == 0 and steps_done == 1 and noticed is not None, results     # no second step was completed alone
