@@ -65,19 +65,26 @@ _SIGS = {
 }
 
 
+def load(path):
+    """Load the library from `path` and make it the one every call of this module uses (e.g. the instrumented
+    build lib/libfp8bs_prof.so).  Raises if the file is missing: there is no other code path."""
+    global _lib
+    if not os.path.exists(path):
+        raise RuntimeError("libfp8bs.so is not built (%s); run `python -m fp8_quant_matmul_b200.build`. "
+                           "There is no fallback implementation." % path)
+    handle = ctypes.CDLL(path)
+    for name, (res, args) in _SIGS.items():
+        fn = getattr(handle, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = handle
+    return _lib
+
+
 def lib():
     """The loaded library.  Raises if it has not been built: there is no other code path."""
-    global _lib
     if _lib is None:
-        if not os.path.exists(_LIB_PATH):
-            raise RuntimeError("libfp8bs.so is not built (%s); run `python -m fp8_quant_matmul_b200.build`. "
-                               "There is no fallback implementation." % _LIB_PATH)
-        handle = ctypes.CDLL(_LIB_PATH)
-        for name, (res, args) in _SIGS.items():
-            fn = getattr(handle, name)
-            fn.restype = res
-            fn.argtypes = args
-        _lib = handle
+        load(_LIB_PATH)
     return _lib
 
 
