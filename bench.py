@@ -418,6 +418,16 @@ def format_kernels_bench(torch, f, dev, hbm_gbs):
     return out
 
 
+_T0 = time.time()
+
+
+def progress(rank, what):
+    """One line per phase on stderr (rank 0 only): where a slow or stuck run spends its time."""
+    if rank == 0:
+        sys.stderr.write("[bench %7.1f s] %s\n" % (time.time() - _T0, what))
+        sys.stderr.flush()
+
+
 def run_gpu_arm(args, rank, world):
     import torch
     import fp8_quant_matmul_b200 as f
@@ -462,6 +472,7 @@ def run_gpu_arm(args, rank, world):
         raise RuntimeError("fp8bs_workspace_init failed")
     torch.cuda.synchronize()
 
+    progress(rank, "set-up done; building and checking the 18 shards")
     # ---- build per-shape benches (this rank's column shard of every shape), each checked against the CPU checker ----
     benches, checked_rows = [], 0
     for i, (M, N, K) in enumerate(SHAPES_18):
@@ -481,6 +492,7 @@ def run_gpu_arm(args, rank, world):
             if events is not None:
                 events[i][1].record()
 
+    progress(rank, "timing the 18 shapes")
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()            # started early: nvidia-smi needs a moment before its first sample
@@ -513,9 +525,11 @@ def run_gpu_arm(args, rank, world):
     per_shape_min = max_over_ranks(per_shape_min)
     per_shape_med = max_over_ranks(per_shape_med)
     f.last_device_status()
+    progress(rank, "isolated launches")
     isolated = max_over_ranks([b.isolated_us() for b in benches])
     f.last_device_status()
 
+    progress(rank, "end to end through host buffers")
     # ---- end to end through the host-buffer entry point ----
     maxM = max(s[0] for s in SHAPES_18)
     maxNl = max(b.nl for b in benches)
@@ -543,6 +557,7 @@ def run_gpu_arm(args, rank, world):
     ctx.close()
     e2e_us = max_over_ranks(e2e_us)
 
+    progress(rank, "M = 16384 variants")
     # ---- M = 16384 variants: aggregate TFLOP/s under the same column partition ----
     shard_widths = [b.nl for b in benches]
     del benches
@@ -577,6 +592,7 @@ def run_gpu_arm(args, rank, world):
     agg_flops = sum(2.0 * 16384 * N * K for (N, K) in NK_PAIRS)
     agg_us = sum(x["us"] for x in m16)
 
+    progress(rank, "all-gather and fused distribution of C")
     # ---- all-gather of the C slabs, timed on its own (not on the GEMM path) ----
     allgather = None
     if dist is not None:
@@ -604,6 +620,7 @@ def run_gpu_arm(args, rank, world):
         fused = fused_distribution_leg(torch, f, h, dist, dev, rank, world, barrier, max_over_ranks, reduce_over_ranks,
                                        plan_n_shards)
 
+    progress(rank, "quantiser / re-encoding kernels")
     formats = format_kernels_bench(torch, f, dev, peaks["hbm_gbs"]) if rank == 0 else None
     torch.cuda.synchronize()
     if rank != 0:
@@ -664,6 +681,7 @@ def run_gpu_arm(args, rank, world):
                              "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(gbs / peaks["hbm_gbs"], 4),
                              "per": "GPU", "peak_source": "hbm_gbs of %s (copy bandwidth); of %s" % (peak_src, of_what),
                              "frac_of_nominal_8000": round(gbs / NOMINAL_HBM_GBS, 4)})
+    progress(rank, "CPU baseline")
     cpu = cpu_sweep(CPU_ROWS)
     line = {
         "metric": "geomean_latency_us_18_shapes", "value": round(geomean(per_shape_us), 3), "unit": "us",
@@ -690,6 +708,7 @@ def run_gpu_arm(args, rank, world):
         "fused_c_distribution": fused,
         "format_kernels": formats,
     }
+    progress(rank, "done")
     emit(line)
     if dist is not None:
         dist.destroy_process_group()
