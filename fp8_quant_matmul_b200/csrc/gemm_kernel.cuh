@@ -497,10 +497,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     }
                     // the promotion warps wait on this one; the producer is several stages ahead
                     if constexpr (CG == 2) {
+#ifdef FP8BS_PAIR_PLAIN_COMMITS
                         ptx::mma_commit_pair(tfull_bar(b) + peer_base);
                         ptx::mma_commit_pair(tfull_bar(b));
                         ptx::mma_commit_pair(empty_bar(s));
                         ptx::mma_commit_pair(empty_bar(s) + peer_base);
+#else
+                        // one commit per barrier reaches both CTAs of the pair (a fourth plain commit per K block costs
+                        // ~100 cycles of tensor-pipe time)
+                        ptx::mma_commit_pair_all(tfull_bar(b), 3);
+                        ptx::mma_commit_pair_all(empty_bar(s), 3);
+#endif
                     } else {
                         ptx::mma_commit(tfull_bar(b));
                         ptx::mma_commit(empty_bar(s));

@@ -222,6 +222,15 @@ __device__ __forceinline__ void mma_commit_pair(uint32_t bar_cluster_addr)
                  : "memory");
 }
 
+// The same arrival delivered to the barrier at this shared-memory offset in every CTA named in `cta_mask` (bit r = CTA
+// rank r of the cluster): one instruction instead of one commit per CTA.  A commit, not a copy: no data is multicast.
+__device__ __forceinline__ void mma_commit_pair_all(uint32_t bar, uint16_t cta_mask)
+{
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(cta_mask)
+                 : "memory");
+}
+
 // ---------------------------------------------------------------- dependent launch --
 // Programmatic dependent launch: a kernel launched with the programmatic-stream-serialization attribute may start
 // while the kernel before it in the stream is still finishing.  grid_dependency_wait() blocks until that earlier
