@@ -43,6 +43,28 @@ def test_every_destination_receives_every_shard(shape, shards, ndest):
         assert bad == 0, "%d mismatches, first %d, max err %g" % (bad, first, maxerr)
 
 
+def test_pair_tile_stores_to_every_destination():
+    # a column shard large enough for the dispatcher to pick the 256 x 256 CTA-pair tile (long K): both CTAs of a pair
+    # store their own 128 rows into every destination
+    M, N, K, shards = 2048, 2560, 4096, 2
+    assert f.select_path(M, N // shards, K)[2] & f.TILE_PAIR
+    A, B, a_s, b_s = h.make_inputs(M, N, K, seed=45)
+    rows = np.arange(5, M, 37, dtype=np.int32)
+    ref = h.oracle_gemm(A, B, a_s, b_s, M, N, K, rows=rows)
+    dA = torch.from_numpy(A).to(dev())
+    dAs, dBs = torch.from_numpy(a_s).to(dev()), torch.from_numpy(b_s).to(dev())
+    dests = [torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev()) for _ in range(2)]
+    Bm = B.reshape(K, N)
+    for (n0, nl) in plan_n_shards(N, shards):
+        dB = torch.from_numpy(np.ascontiguousarray(Bm[:, n0:n0 + nl]).ravel()).to(dev())
+        f.gemm_scatter(dA, dB, dAs, dBs, dests, M, nl, K, n0, N)
+    f.last_device_status()
+    for d in dests:
+        assert not torch.isnan(d).any()
+        bad, first, maxerr = h.mismatches(ref, d.view(torch.int16).cpu().numpy().view(np.uint16)[rows])
+        assert bad == 0, "%d mismatches, first %d, max err %g" % (bad, first, maxerr)
+
+
 def test_scatter_argument_errors():
     M, N, K = 128, 256, 256
     z8 = torch.zeros(M * K, dtype=torch.uint8, device=dev())
