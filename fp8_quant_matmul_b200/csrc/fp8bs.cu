@@ -521,6 +521,7 @@ static int gemm_impl(const void* A, const void* B, const float* a_scale, const f
     p.sn = ceil_div(n_total, 128);
     p.m_tiles = ceil_div(M, 128 * cfg.cg);
     p.n_tiles = ceil_div(N, cfg.tile_n);
+    p.inv_m_tiles = 1.0f / static_cast<float>(p.m_tiles);
     p.splits = cfg.splits;
     p.n_dest = dests ? n_dest : 1;
     p.elem_scale = 1.0f;

@@ -89,6 +89,7 @@ struct GemmParams {
     int n_off;               // global column index of local column 0 (N-sharded calls), else 0
     int sn;                  // rows of b_scale = ceil(N_total / 128)  (check.cu:36)
     int m_tiles, n_tiles, splits;
+    float inv_m_tiles;       // 1 / m_tiles, for the tile -> (row block, column block) decode
     int n_dest;              // number of valid entries of the CMaps argument (1 = only the caller's C)
     float elem_scale;        // folded into b_scale: 1 for e4m3fn bytes
 #ifdef FP8BS_PROFILE
@@ -233,13 +234,15 @@ struct FloatCols {
 // box laid out as the 128-byte-swizzled TMA store expects; then the warp's lane 0 issues the store.
 // The box covers rows [row0, row0 + 32) and columns [col, col + 64); lane = row within the box.
 // PENDING: how many of this thread's most recent stores may still be reading shared memory (1 when the warp
-// alternates between two boxes: only the store before the last one used this box).
+// alternates between two boxes: only the store before the last one used this box); negative: the caller has waited.
 template <int PENDING, class Cols>
 __device__ __forceinline__ void stage_and_store_64(const CUtensorMap* tmC, int n_dest, uint8_t* stg, uint32_t stg_addr,
                                                    int lane, const Cols cols, int col, int row0, int M, int N)
 {
-    if (lane == 0) ptx::tma_store_wait_read<PENDING>();      // the previous store out of this box has read it
-    __syncwarp();
+    if constexpr (PENDING >= 0) {
+        if (lane == 0) ptx::tma_store_wait_read<PENDING>();  // the previous store out of this box has read it
+        __syncwarp();
+    }
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
         uint4 q;
@@ -255,6 +258,38 @@ __device__ __forceinline__ void stage_and_store_64(const CUtensorMap* tmC, int n
     if (lane == 0 && col < N && row0 < M) {
         // rows >= M and columns >= N are clipped by the hardware; one bulk group covers every destination's copy
         for (int d = 0; d < n_dest; ++d) ptx::tma_store_2d(tmC + d, stg_addr, col, row0);
+        ptx::tma_store_commit();
+    }
+}
+
+// The two 64-column boxes of a warp's 32 x 128 piece at once: both are staged, then lanes 0 and 1 issue one store each
+// in the same instruction, so the warp pays the issue latency of a TMA store once per tile instead of twice (1-3 % on
+// the shapes with many tiles per CTA).  Bulk groups belong to the issuing thread: lane h issues, and waits for, the
+// stores out of box h.  The caller has made sure that both boxes are free (wait_read<0> in lanes 0 and 1).
+template <class Cols0, class Cols1>
+__device__ __forceinline__ void stage_and_store_2x64(const CUtensorMap* tmC, int n_dest, uint8_t* stg, uint32_t stg_addr,
+                                                     int lane, const Cols0 c0, const Cols1 c1, int col, int row0, int M, int N)
+{
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            uint4 q;
+            if (h == 0) {
+                q.x = c0.bf16_pair(4 * j + 0); q.y = c0.bf16_pair(4 * j + 1);
+                q.z = c0.bf16_pair(4 * j + 2); q.w = c0.bf16_pair(4 * j + 3);
+            } else {
+                q.x = c1.bf16_pair(4 * j + 0); q.y = c1.bf16_pair(4 * j + 1);
+                q.z = c1.bf16_pair(4 * j + 2); q.w = c1.bf16_pair(4 * j + 3);
+            }
+            *reinterpret_cast<uint4*>(stg + h * 4096 + lane * 128 + ((j ^ (lane & 7)) << 4)) = q;
+        }
+    }
+    ptx::fence_proxy_async_smem();
+    __syncwarp();
+    const int mycol = col + lane * 64;
+    if (lane < 2 && mycol < N && row0 < M) {
+        for (int d = 0; d < n_dest; ++d) ptx::tma_store_2d(tmC + d, stg_addr + lane * 4096, mycol, row0);
         ptx::tma_store_commit();
     }
 }
@@ -400,8 +435,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             kb0 = SPLITK ? (split * KB) / p.splits : 0;
             kb1 = SPLITK ? ((split + 1) * KB) / p.splits : KB;
         }
-        m0 = (tile % p.m_tiles) * Cfg::TILE_M + static_cast<int>(rank) * Cfg::BM;
-        n0 = (tile / p.m_tiles) * BN;
+        // tile = ni * m_tiles + mi without an integer division (some 100 cycles, twice per tile in every role): the
+        // float quotient is off by at most one for tile counts below 2^22, and the remainder says which way
+        int ni = __float2int_rz(__int2float_rn(tile) * p.inv_m_tiles);
+        int mi = tile - ni * p.m_tiles;
+        if (mi < 0) { --ni; mi += p.m_tiles; }
+        else if (mi >= p.m_tiles) { ++ni; mi -= p.m_tiles; }
+        m0 = mi * Cfg::TILE_M + static_cast<int>(rank) * Cfg::BM;
+        n0 = ni * BN;
     };
 
     if (warp < 4) {
@@ -682,12 +723,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
             // ---- epilogue of a finished tile: fp32 -> bf16 (round to nearest even), staged, TMA store ----
             auto store_tile = [&]() {
-#pragma unroll
-                for (int h = 0; h < Cfg::COLS / 64; ++h) {
-                    const int box = (Cfg::NSTG == 2) ? h : 0;
-                    stage_and_store_64<Cfg::NSTG - 1>(cmaps.m, p.n_dest, my_stg + box * 4096, my_stg_addr + box * 4096, lane,
-                                                      PackedCols{acc[2 * h], acc[2 * h + 1]}, ncol0 + h * 64,
-                                                      m0 + quarter * 32, p.M, p.N);
+                if constexpr (Cfg::NSTG == 2) {
+                    // box h belongs to lane h: its previous store has read the box before anything is staged into it
+                    if (lane < 2) ptx::tma_store_wait_read<0>();
+                    __syncwarp();
+                    if (u + unit_step < units) {
+                        stage_and_store_2x64(cmaps.m, p.n_dest, my_stg, my_stg_addr, lane, PackedCols{acc[0], acc[1]},
+                                             PackedCols{acc[2], acc[3]}, ncol0, m0 + quarter * 32, p.M, p.N);
+                    } else {
+                        // the CTA's last tile: the first store leaves while the second box is being staged (shorter tail)
+                        stage_and_store_64<-1>(cmaps.m, p.n_dest, my_stg, my_stg_addr, lane, PackedCols{acc[0], acc[1]},
+                                               ncol0, m0 + quarter * 32, p.M, p.N);
+                        stage_and_store_64<-1>(cmaps.m, p.n_dest, my_stg + 4096, my_stg_addr + 4096, lane,
+                                               PackedCols{acc[2], acc[3]}, ncol0 + 64, m0 + quarter * 32, p.M, p.N);
+                    }
+                } else {
+                    stage_and_store_64<0>(cmaps.m, p.n_dest, my_stg, my_stg_addr, lane, PackedCols{acc[0], acc[1]}, ncol0,
+                                          m0 + quarter * 32, p.M, p.N);
                 }
             };
             if constexpr (MODE == 0) {
@@ -853,7 +905,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (pw == 0 && lane == 0) { PROF_OUT(4, w_sfull); PROF_OUT(5, w_tfull); PROF_OUT(6, t_fma); PROF_OUT(7, t_epi); PROF_STAMP(13); }
 #endif
         // C must have been read out of shared memory before the CTA goes away
-        if (lane == 0) ptx::tma_store_wait_read<0>();
+        if (lane < 2) ptx::tma_store_wait_read<0>();
         __syncwarp();
     }
 
