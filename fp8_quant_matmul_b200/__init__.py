@@ -16,6 +16,7 @@ from .api import (  # noqa: F401
     TILE_PAIR,
     SPLIT_WORKSPACE,
     STREAM_K,
+    SHORT_K,
     gemm,
     gemm_ref,
     gemm_mn_small_static,

@@ -15,6 +15,7 @@ PATH_AUTO, PATH_MN_LARGE, PATH_MN_SMALL = 0, 1, 2
 TILE_PAIR = 0x1000      # tile_n = 256 | TILE_PAIR: a 256 x 256 tile owned by a pair of CTAs
 SPLIT_WORKSPACE = 0x2000  # OR into tile_n: reduce split-K partial sums through the workspace, not in a cluster
 STREAM_K = 0x4000         # OR into tile_n: deal the K blocks of all tiles out evenly over the SMs (needs the workspace)
+SHORT_K = 0x8000          # OR into tile_n (0 or 256): K <= 256, both K blocks of a tile stay in tensor memory
 
 # The 18 benchmark shapes (M, N, K) of the reference's results table (README.md:15-25).
 SHAPES_18 = [(m, n, k) for m in (1024, 6144)

@@ -137,7 +137,8 @@ static int device_setup(DeviceInfo** out)
             (rc = prepare_kernel<256, 2, 0>()) || (rc = prepare_kernel<128, 1, 1>()) ||
             (rc = prepare_kernel<256, 1, 1>()) || (rc = prepare_kernel<256, 2, 1>()) ||
             (rc = prepare_kernel<128, 1, 2>()) || (rc = prepare_kernel<256, 1, 2>()) ||
-            (rc = prepare_kernel<128, 1, 3>()) || (rc = prepare_kernel<256, 1, 3>())) {
+            (rc = prepare_kernel<128, 1, 3>()) || (rc = prepare_kernel<256, 1, 3>()) ||
+            (rc = prepare_kernel<256, 1, 4>())) {
             d.status = rc;
             return rc;
         }
@@ -199,7 +200,8 @@ struct Config {
     int splits;   // 1 for mn_large
     int cg;       // 1: a CTA owns 128 rows of a tile; 2: a pair of CTAs owns 256 rows
     int mode;     // 0 full K; 1 split-K reduced through a workspace; 2 split-K reduced inside a cluster;
-                  // 3 stream-K: the K blocks of all tiles dealt out evenly over `ctas` CTAs
+                  // 3 stream-K: the K blocks of all tiles dealt out evenly over `ctas` CTAs; 4 short K (K <= 256):
+                  // full K with both K blocks of a tile resident in TMEM
     int ctas;     // mode 3 only
 };
 
@@ -236,6 +238,8 @@ static int stream_k_ctas(int tiles, int KB, int sm_count)
 // are also on tiles far apart and share less through L2.  Measured 6-11 us in total on the benchmark shapes, which
 // is why the estimate keeps stream-K for shapes with very few, very long tiles only.
 constexpr double STREAM_K_FIXUP_US = 6.0;
+// Mode 4 (K <= 256, partial sums resident in TMEM) is chosen by rule, see choose_config.
+constexpr int SHORT_K_MAX_WAVES = 4;
 static double config_cost(const DeviceModel& dm, int M, int N, int K, int tile_n, int splits, int cg, int mode)
 {
     const int KB = K / 128;
@@ -278,9 +282,19 @@ static Config choose_config(const DeviceModel& dm, int M, int N, int K, int path
     const int KB = K / 128;
     const bool force_ws = (tile_n & FP8BS_SPLIT_WORKSPACE) != 0;
     const bool force_sk = (tile_n & FP8BS_STREAM_K) != 0;
-    const int want_tile = tile_n & ~(FP8BS_SPLIT_WORKSPACE | FP8BS_STREAM_K);
+    const int want_tile = tile_n & ~(FP8BS_SPLIT_WORKSPACE | FP8BS_STREAM_K | FP8BS_SHORT_K);
     Config best{FP8BS_PATH_MN_LARGE, 128, 1, 1, 0, 0};
     double best_cost = 1e300;
+    // short K: the tile's partial sums stay in TMEM (mode 4), a member of the mn_large family (K is not cut)
+    if (tile_n & FP8BS_SHORT_K) return Config{FP8BS_PATH_MN_LARGE, 256, 1, 1, 4, 0};
+    if (KB <= 2 && path != FP8BS_PATH_MN_SMALL && splits <= 1 && !force_ws && !force_sk && want_tile == 0) {
+        // Measured on a B200: 5-6 % faster than the full-K kernel at K = 128 and, at K = 256, up to about four tiles
+        // per SM (1024 x 7168 x 256: 7.20 against 7.64 us); with more tiles both kernels write C as fast as the
+        // memory takes it and the full-K kernel, which overlaps the MMAs of a tile with the scaling of the one
+        // before, is 3 % ahead (6144 x 7168 x 256: 23.7 against 24.4 us).
+        const int tiles = ceil_div(M, 128) * ceil_div(N, 256);
+        if (KB == 1 || tiles <= SHORT_K_MAX_WAVES * dm.sm_count) return Config{FP8BS_PATH_MN_LARGE, 256, 1, 1, 4, 0};
+    }
     // stream-K: a member of the mn_small family (it cuts K), chosen when it is asked for or when the caller left
     // both path and splits open
     if (force_sk || (path != FP8BS_PATH_MN_LARGE && splits == 0 && !force_ws)) {
@@ -344,8 +358,11 @@ static int check_args(int M, int N, int K, int n0, int n_total, int path, int sp
     if (splits < 0 || splits > K / 128 || splits > MAX_SPLITS) return FP8BS_ERR_ARG;
     if (path == FP8BS_PATH_MN_LARGE && splits > 1) return FP8BS_ERR_ARG;
     {
-        const int t = tile_n & ~(FP8BS_SPLIT_WORKSPACE | FP8BS_STREAM_K);
+        const int t = tile_n & ~(FP8BS_SPLIT_WORKSPACE | FP8BS_STREAM_K | FP8BS_SHORT_K);
         if (t != 0 && t != 128 && t != 256 && t != (256 | FP8BS_TILE_PAIR)) return FP8BS_ERR_ARG;
+        if ((tile_n & FP8BS_SHORT_K) && ((t != 0 && t != 256) || (tile_n & (FP8BS_SPLIT_WORKSPACE | FP8BS_STREAM_K)) ||
+                                         splits > 1 || path == FP8BS_PATH_MN_SMALL || K > 256))
+            return FP8BS_ERR_ARG;
         if ((tile_n & FP8BS_STREAM_K) && ((tile_n & (FP8BS_TILE_PAIR | FP8BS_SPLIT_WORKSPACE)) || splits > 1 ||
                                           path == FP8BS_PATH_MN_LARGE))
             return FP8BS_ERR_ARG;
@@ -455,6 +472,7 @@ static int launch_config(const Config& c, const TensorMaps& tm, const GemmParams
         if (c.cg == 2) return launch<256, 2, 1>(tm, p, sm_count, st);
         return c.tile_n == 256 ? launch<256, 1, 1>(tm, p, sm_count, st) : launch<128, 1, 1>(tm, p, sm_count, st);
     }
+    if (c.mode == 4) return launch<256, 1, 4>(tm, p, sm_count, st);
     if (c.cg == 2) return launch<256, 2, 0>(tm, p, sm_count, st);
     return c.tile_n == 256 ? launch<256, 1, 0>(tm, p, sm_count, st) : launch<128, 1, 0>(tm, p, sm_count, st);
 }
@@ -758,7 +776,7 @@ int fp8bs_select_path(int M, int N, int K, int* splits, int* tile_n)
     if (rc) return rc;
     const Config c = choose_config(host_model(), M, N, K, FP8BS_PATH_AUTO, 0, 0);
     if (splits) *splits = c.splits;
-    if (tile_n) *tile_n = c.tile_n | (c.cg == 2 ? FP8BS_TILE_PAIR : 0) | (c.mode == 1 ? FP8BS_SPLIT_WORKSPACE : 0) |
+    if (tile_n) *tile_n = c.tile_n | (c.cg == 2 ? FP8BS_TILE_PAIR : 0) | (c.mode == 1 ? FP8BS_SPLIT_WORKSPACE : 0) | (c.mode == 4 ? FP8BS_SHORT_K : 0) |
                           (c.mode == 3 ? FP8BS_STREAM_K : 0);
     return c.path;
 }
@@ -770,7 +788,7 @@ int fp8bs_select_path_sms(int M, int N, int K, int sm_count, int* splits, int* t
     if (sm_count < 1) return FP8BS_ERR_ARG;
     const Config c = choose_config(scaled_model(sm_count), M, N, K, FP8BS_PATH_AUTO, 0, 0);
     if (splits) *splits = c.splits;
-    if (tile_n) *tile_n = c.tile_n | (c.cg == 2 ? FP8BS_TILE_PAIR : 0) | (c.mode == 1 ? FP8BS_SPLIT_WORKSPACE : 0) |
+    if (tile_n) *tile_n = c.tile_n | (c.cg == 2 ? FP8BS_TILE_PAIR : 0) | (c.mode == 1 ? FP8BS_SPLIT_WORKSPACE : 0) | (c.mode == 4 ? FP8BS_SHORT_K : 0) |
                           (c.mode == 3 ? FP8BS_STREAM_K : 0);
     if (ctas) {
         // CTAs that have to be resident together: stream-K's whole grid, one cluster for the cluster reduction,

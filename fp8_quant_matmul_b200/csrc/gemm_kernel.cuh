@@ -23,6 +23,10 @@
 //           3 stream-K: the K blocks of all tiles are dealt out evenly over the CTAs; a tile that
 //                 falls to several CTAs is finished by the one that holds its first K block, from
 //                 partial tiles the others leave in the workspace (added in K order).
+//           4 short K (K <= 256, 256-wide tiles): the partial sums of both K blocks of a tile stay in the two TMEM
+//                 buffers and are handed over once per tile; a promotion thread reads both K blocks of 64 of its
+//                 columns with two loads in flight, scales and adds them in registers and stages the result, then the
+//                 other 64.  One barrier round trip per tile instead of one per K block, and no running sums.
 // The epilogue stores a finished tile to one or several destinations (CMaps): the caller's C, and
 // for the fused distribution of an N-sharded GEMM the peer-mapped C of the other GPUs.
 //
@@ -235,6 +239,23 @@ struct FloatCols {
 // The box covers rows [row0, row0 + 32) and columns [col, col + 64); lane = row within the box.
 // PENDING: how many of this thread's most recent stores may still be reading shared memory (1 when the warp
 // alternates between two boxes: only the store before the last one used this box); negative: the caller has waited.
+// Converts 64 columns of this thread's row to bf16 (round to nearest even) into row `lane` of a 32-row x 128-byte
+// staging box, laid out as the 128-byte-swizzled TMA store expects.
+template <class Cols>
+__device__ __forceinline__ void stage_64(uint8_t* stg, int lane, const Cols cols)
+{
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        uint4 q;
+        q.x = cols.bf16_pair(4 * j + 0);
+        q.y = cols.bf16_pair(4 * j + 1);
+        q.z = cols.bf16_pair(4 * j + 2);
+        q.w = cols.bf16_pair(4 * j + 3);
+        // 16-byte chunk j, XOR-swizzled with the row index (bank-conflict free)
+        *reinterpret_cast<uint4*>(stg + lane * 128 + ((j ^ (lane & 7)) << 4)) = q;
+    }
+}
+
 template <int PENDING, class Cols>
 __device__ __forceinline__ void stage_and_store_64(const CUtensorMap* tmC, int n_dest, uint8_t* stg, uint32_t stg_addr,
                                                    int lane, const Cols cols, int col, int row0, int M, int N)
@@ -243,16 +264,7 @@ __device__ __forceinline__ void stage_and_store_64(const CUtensorMap* tmC, int n
         if (lane == 0) ptx::tma_store_wait_read<PENDING>();  // the previous store out of this box has read it
         __syncwarp();
     }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        uint4 q;
-        q.x = cols.bf16_pair(4 * j + 0);
-        q.y = cols.bf16_pair(4 * j + 1);
-        q.z = cols.bf16_pair(4 * j + 2);
-        q.w = cols.bf16_pair(4 * j + 3);
-        // row `lane` of the box, 16-byte chunk j, XOR-swizzled with the row index (bank-conflict free)
-        *reinterpret_cast<uint4*>(stg + lane * 128 + ((j ^ (lane & 7)) << 4)) = q;
-    }
+    stage_64(stg, lane, cols);
     ptx::fence_proxy_async_smem();
     __syncwarp();
     if (lane == 0 && col < N && row0 < M) {
@@ -270,21 +282,8 @@ template <class Cols0, class Cols1>
 __device__ __forceinline__ void stage_and_store_2x64(const CUtensorMap* tmC, int n_dest, uint8_t* stg, uint32_t stg_addr,
                                                      int lane, const Cols0 c0, const Cols1 c1, int col, int row0, int M, int N)
 {
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            uint4 q;
-            if (h == 0) {
-                q.x = c0.bf16_pair(4 * j + 0); q.y = c0.bf16_pair(4 * j + 1);
-                q.z = c0.bf16_pair(4 * j + 2); q.w = c0.bf16_pair(4 * j + 3);
-            } else {
-                q.x = c1.bf16_pair(4 * j + 0); q.y = c1.bf16_pair(4 * j + 1);
-                q.z = c1.bf16_pair(4 * j + 2); q.w = c1.bf16_pair(4 * j + 3);
-            }
-            *reinterpret_cast<uint4*>(stg + h * 4096 + lane * 128 + ((j ^ (lane & 7)) << 4)) = q;
-        }
-    }
+    stage_64(stg, lane, c0);
+    stage_64(stg + 4096, lane, c1);
     ptx::fence_proxy_async_smem();
     __syncwarp();
     const int mycol = col + lane * 64;
@@ -325,6 +324,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     constexpr bool STREAMK = (MODE == 3);               // K blocks of all tiles dealt out evenly, see below
     static_assert(MODE != 2 || CG == 1, "the cluster reduction uses the cluster for the K splits");
     static_assert(MODE != 3 || CG == 1, "stream-K is built for single-CTA tiles");
+    constexpr bool RESIDENT = (MODE == 4);              // both K blocks of a tile kept in TMEM (K <= 256)
+    static_assert(!RESIDENT || (CG == 1 && BN == 256), "the short-K mode uses 256-wide single-CTA tiles");
     // MODE 2: fp32 partial tile of this CTA, rows padded by 16 bytes so that a warp's 32 rows hit distinct banks
     constexpr int PART_PITCH = BN * 4 + 16;
     static_assert(MODE != 2 || 128 * PART_PITCH <= STAGES * Cfg::STAGE_BYTES, "partial tile must fit in the stage area");
@@ -493,7 +494,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         } else if (warp == 1 && lane == 0 && rank == 0) {
             // ---------------------------------------------------- MMA issuer ----------------
             constexpr uint32_t idesc = ptx::make_idesc_e4m3_mnmajor(Cfg::TILE_M, BN);
-            uint32_t it = 0, ait = 0;
+            uint32_t it = 0, ait = 0, tcount = 0;
             bool ok = true;
             PROF_DECL(w_tempty); PROF_DECL(w_full); PROF_DECL(t_mma_total);
 #ifdef FP8BS_PROFILE
@@ -507,8 +508,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 for (int kb = kb0; kb < kb1; ++kb, ++it, ++ait) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1u;
-                    const int b = ait % NBUF;
-                    const uint32_t bph = (ait / NBUF) & 1u;
+                    // MODE 4: K block j of a tile goes to buffer j; the pair is handed over and taken back once per tile
+                    // (barriers tfull / tempty number 0, phase = tile count)
+                    const int b = RESIDENT ? (kb - kb0) : static_cast<int>(ait % NBUF);
+                    const uint32_t bph = RESIDENT ? (tcount & 1u) : ((ait / NBUF) & 1u);
+                    const int eb = RESIDENT ? 0 : b;                       // the barrier pair that guards this buffer
                     // operands first (they are usually there already), then the TMEM buffer: nothing but the MMA
                     // issue stands between the promotion warps' release of the buffer and its reuse
                     { PROF_T0();
@@ -516,9 +520,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     PROF_ADD(w_full); }
                     if (!ok) break;
                     PROF_TRACE(1, it);
-                    { PROF_T0();
-                    ok = wait_bounded(tempty_bar(b), bph ^ 1u, abort_flag, p.status, DS_TIMEOUT_TMEM_EMPTY);
-                    PROF_ADD(w_tempty); }
+                    if (!RESIDENT || kb == kb0) {
+                        PROF_T0();
+                        ok = wait_bounded(tempty_bar(eb), bph ^ 1u, abort_flag, p.status, DS_TIMEOUT_TMEM_EMPTY);
+                        PROF_ADD(w_tempty);
+                    }
                     if (!ok) break;
                     PROF_TRACE(0, it);
 #ifdef FP8BS_PROFILE
@@ -550,11 +556,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                         ptx::mma_commit_pair_all(empty_bar(s), 3);
 #endif
                     } else {
-                        ptx::mma_commit(tfull_bar(b));
+                        if (!RESIDENT || kb == kb1 - 1) ptx::mma_commit(tfull_bar(eb));
                         ptx::mma_commit(empty_bar(s));
                     }
                     PROF_TRACE(2, it);
                 }
+                ++tcount;
             }
 #ifdef FP8BS_PROFILE
             t_mma_total = clock64() - mma_start;
@@ -592,6 +599,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if constexpr (CG == 2) lead_tempty = ptx::mapa(tempty_bar(0), 0);
         uint32_t ait = 0;
         uint32_t sgit = 0;                       // a_scale ring entries consumed so far
+        uint32_t tcount = 0;                     // MODE 4: tiles done by this CTA
         bool ok = true;
         PROF_DECL(w_sfull); PROF_DECL(w_tfull); PROF_DECL(t_fma); PROF_DECL(t_epi);
         // b_scale lane vectors of unit u: K blocks kb0 + lane and kb0 + 32 + lane of the one or two 128-column blocks
@@ -643,6 +651,77 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             };
             float bl_vec = pf_bl, bh_vec = pf_bh, bl_nxt = pf_bln, bh_nxt = pf_bhn;
 
+            if constexpr (RESIDENT) {
+                // ---- short K: both K blocks of the tile are in TMEM when the MMA warp hands it over ----
+                const bool two = (kb1 - kb0) > 1;
+                const float bl0 = __shfl_sync(0xffffffffu, bl_vec, 0) * p.elem_scale;
+                const float bh0 = __shfl_sync(0xffffffffu, bh_vec, 0) * p.elem_scale;
+                const float bl1 = __shfl_sync(0xffffffffu, bl_vec, 1) * p.elem_scale;
+                const float bh1 = __shfl_sync(0xffffffffu, bh_vec, 1) * p.elem_scale;
+                if (u + unit_step < units) fetch_bscale(u + unit_step);      // in flight during everything below
+                const int si = sgit % SRING;
+                ok = wait_bounded(sfull_bar(si), (sgit / SRING) & 1u, abort_flag, p.status, DS_TIMEOUT_SCALE_FULL);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                const float as0 = sring_ptr[(si * Cfg::SGRP + 0) * 128 + row_in_tile];   // entry released below
+                const float as1 = sring_ptr[(si * Cfg::SGRP + 1) * 128 + row_in_tile];   // 0 when K = 128 (zero fill)
+                // same arithmetic as the K loop of the other modes: acc = fma(p0, s0, 0), then acc = fma(p1, s1, acc)
+                const float s0l = as0 * bl0, s0h = as0 * bh0, s1l = as1 * bl1, s1h = as1 * bh1;
+                const unsigned long long s0l2 = pack_f32x2(s0l, s0l), s0h2 = pack_f32x2(s0h, s0h);
+                const unsigned long long s1l2 = pack_f32x2(s1l, s1l), s1h2 = pack_f32x2(s1h, s1h);
+                // box h belongs to lane h: its previous store has read the box before anything is staged into it
+                if (lane < 2) ptx::tma_store_wait_read<0>();
+                ok = wait_bounded(tfull_bar(0), tcount & 1u, abort_flag, p.status, DS_TIMEOUT_TMEM_FULL);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                ptx::tc_fence_after_sync();
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                                       static_cast<uint32_t>(grp * Cfg::COLS);
+                const bool last_unit = !(u + unit_step < units);
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    uint32_t v0[64], v1[64];
+                    if (two) ptx::tmem_ld_2x64_sync(taddr + h * 64, taddr + BN + h * 64, v0, v1);
+                    else ptx::tmem_ld_x64_sync(taddr + h * 64, v0);
+                    if (h == 1) {
+                        // the whole tile is in registers or staged: the MMA warp may fill TMEM for the next tile
+                        ptx::tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(tempty_bar(0));
+                    }
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) { acc[0][i] = 0ull; acc[1][i] = 0ull; }
+                    ptx::fma32_from64<0>(acc[0], v0, (2 * h >= hi_from) ? s0h2 : s0l2);
+                    ptx::fma32_from64<32>(acc[1], v0, (2 * h + 1 >= hi_from) ? s0h2 : s0l2);
+                    if (two) {
+                        ptx::fma32_from64<0>(acc[0], v1, (2 * h >= hi_from) ? s1h2 : s1l2);
+                        ptx::fma32_from64<32>(acc[1], v1, (2 * h + 1 >= hi_from) ? s1h2 : s1l2);
+                    }
+                    if (last_unit) {
+                        // the CTA's last tile: each store leaves as soon as its box is staged (shorter tail)
+                        stage_and_store_64<-1>(cmaps.m, p.n_dest, my_stg + h * 4096, my_stg_addr + h * 4096, lane,
+                                               PackedCols{acc[0], acc[1]}, ncol0 + h * 64, m0 + quarter * 32, p.M, p.N);
+                    } else {
+                        stage_64(my_stg + h * 4096, lane, PackedCols{acc[0], acc[1]});
+                    }
+                }
+                if (!last_unit) {
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    const int mycol = ncol0 + lane * 64;
+                    if (lane < 2 && mycol < p.N && m0 + quarter * 32 < p.M) {
+                        for (int d = 0; d < p.n_dest; ++d)
+                            ptx::tma_store_2d(cmaps.m + d, my_stg_addr + lane * 4096, mycol, m0 + quarter * 32);
+                        ptx::tma_store_commit();
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(sempty_bar(si));
+                ++sgit;
+                ++tcount;
+                continue;                                                     // next tile
+            }
+            if constexpr (!RESIDENT)
             for (int kb = kb0; kb < kb1 && ok; ++kb, ++ait) {
                 const int kj = (kb - kb0) & 31;
                 if (kj == 0 && kb != kb0) {

@@ -64,6 +64,10 @@ extern "C" {
  * library when path and splits are left open and it is estimated fastest; OR this flag into tile_n (128 or 256, or 0)
  * to force it.  Needs the workspace (fp8bs_workspace_bytes_ex), splits must be 0 or 1. */
 #define FP8BS_STREAM_K       0x4000
+/* Short K (K <= 256): 256-wide tiles whose partial sums of both 128-K blocks stay in tensor memory and are handed to
+ * the scaling warps once per tile instead of once per block.  Chosen by the library for such shapes when it is
+ * estimated fastest; OR this flag into tile_n (256 or 0) to force it (path auto or mn_large, splits 0 or 1). */
+#define FP8BS_SHORT_K        0x8000
 
 /* ---- the operator ---------------------------------------------------------------- */
 

@@ -59,7 +59,8 @@ FORCED = [
 
 def ids(cfgs):
     return ["p%d-s%d-t%d%s%s" % (c["path"], c["splits"], c["tile_n"] & 0xFFF, "pair" if c["tile_n"] & f.TILE_PAIR else "",
-                                 "ws" if c["tile_n"] & f.SPLIT_WORKSPACE else ("sk" if c["tile_n"] & f.STREAM_K else ""))
+                                 "ws" if c["tile_n"] & f.SPLIT_WORKSPACE else ("sk" if c["tile_n"] & f.STREAM_K else
+                                                                                 ("short" if c["tile_n"] & f.SHORT_K else "")))
             for c in cfgs]
 
 
@@ -102,6 +103,56 @@ def test_kat_one_hot_pins_index_formulas(cfg):
         got = run_gemm(A, B, a_s, b_s, M, N, K, **cfg)
         assert_parity(h.oracle_gemm(A, B, a_s, b_s, M, N, K), got, "one-hot %s" % ((m, n, k),))
         assert np.count_nonzero(h.bf16_bits_to_f32(got)) == 1 and h.bf16_bits_to_f32(got)[m, n] != 0
+
+
+# ------------------------------------------------------------------ short K (K <= 256) ------
+SHORT = dict(path=f.PATH_MN_LARGE, splits=1, tile_n=f.SHORT_K)      # a tile's partial sums stay in tensor memory
+SHORT_K_SHAPES = [(128, 128, 128), (128, 128, 256), (16, 16, 128), (144, 80, 256), (128, 64, 256), (512, 1024, 256),
+                  (2048, 2064, 256), (1024, 7168, 256), (1024, 7168, 128)]
+
+
+@pytest.mark.parametrize("shape", SHORT_K_SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_short_k_kernel_matches_the_oracle_and_the_full_k_kernel_bit_for_bit(shape):
+    M, N, K = shape
+    A, B, a_s, b_s = h.make_inputs(M, N, K, seed=300 + M + N + K)
+    got = run_gemm(A, B, a_s, b_s, M, N, K, **SHORT)
+    assert_parity(h.oracle_gemm(A, B, a_s, b_s, M, N, K), got, "short K %s" % (shape,))
+    # same arithmetic in the same order as the K loop of the other kernels: equal bits, not only equal within tolerance
+    full = run_gemm(A, B, a_s, b_s, M, N, K, path=f.PATH_MN_LARGE, splits=1, tile_n=256)
+    assert np.array_equal(got, full)
+
+
+def test_short_k_kat_small_integers_and_one_hot():
+    M, N, K = 128, 256, 256
+    rng = np.random.default_rng(6)
+    vals = np.array([h.e4m3fn_byte(v) for v in (-2.0, -1.0, 0.0, 1.0, 2.0)], dtype=np.uint8)
+    ai, bi = rng.integers(0, 5, (K, M)), rng.integers(0, 5, (K, N))
+    want = ((ai - 2).T.astype(np.int64) @ (bi - 2).astype(np.int64)).astype(np.float32)
+    got = h.bf16_bits_to_f32(run_gemm(vals[ai].ravel(), vals[bi].ravel(), np.ones(M * 2, np.float32),
+                                      np.ones(2 * 2, np.float32), M, N, K, **SHORT))
+    assert np.array_equal(got, want)
+    # one non-zero in A and in B on a ragged shape: exactly one non-zero in C, scaled by a_scale[m + M*kb] * b_scale[nb + sn*kb]
+    M, N, K = 144, 576, 256
+    sn, KB = 5, 2
+    a_s = 1.0 + np.arange(M * KB, dtype=np.float32) / 64
+    b_s = (0.5 + np.arange(sn * KB, dtype=np.float32)) * 0.25
+    for (m, n, k) in [(0, 0, 0), (143, 575, 255), (7, 513, 130), (130, 127, 127), (3, 128, 128)]:
+        A, B = np.zeros(M * K, np.uint8), np.zeros(N * K, np.uint8)
+        A[m + M * k] = h.e4m3fn_byte(3.0)
+        B[n + N * k] = h.e4m3fn_byte(-1.5)
+        got = run_gemm(A, B, a_s, b_s, M, N, K, **SHORT)
+        assert_parity(h.oracle_gemm(A, B, a_s, b_s, M, N, K), got, "one-hot %s" % ((m, n, k),))
+        assert np.count_nonzero(h.bf16_bits_to_f32(got)) == 1 and h.bf16_bits_to_f32(got)[m, n] != 0
+
+
+def test_short_k_column_shard_uses_the_global_scale_columns():
+    # columns [n0, n0 + nl) of a wider problem: b_scale is indexed by the global column
+    M, N, K, n0, nl = 256, 1024, 256, 192, 448
+    A, B, a_s, b_s = h.make_inputs(M, N, K, seed=77)
+    full = h.oracle_gemm(A, B, a_s, b_s, M, N, K)
+    from fp8_quant_matmul_b200.shard import shard_columns_of_B
+    got = run_gemm(A, shard_columns_of_B(B, N, K, n0, nl), a_s, b_s, M, nl, K, n0=n0, n_total=N, **SHORT)
+    assert_parity(np.ascontiguousarray(full[:, n0:n0 + nl]), got, "short K shard")
 
 
 # ------------------------------------------------------------------ random parity ----------

@@ -43,7 +43,7 @@ def test_dispatch_policy_on_the_18_shapes():
     for (M, N, K) in f.SHAPES_18:
         path, splits, tile_n = f.select_path(M, N, K)
         assert path in (f.PATH_MN_LARGE, f.PATH_MN_SMALL)
-        assert (tile_n & ~(f.SPLIT_WORKSPACE | f.STREAM_K)) in (128, 256, 256 | f.TILE_PAIR)
+        assert (tile_n & ~(f.SPLIT_WORKSPACE | f.STREAM_K | f.SHORT_K)) in (128, 256, 256 | f.TILE_PAIR)
         assert 1 <= splits <= K // 128
         # the mn_small family cuts K: into `splits` ranges per tile, or (stream-K) evenly over the SMs
         assert (path == f.PATH_MN_SMALL) == (splits > 1 or bool(tile_n & f.STREAM_K))
@@ -55,6 +55,10 @@ def test_dispatch_policy_on_the_18_shapes():
     assert f.select_path(1024, 512, 7168)[0] == f.PATH_MN_SMALL
     assert f.select_path(1024, 576, 7168)[0] == f.PATH_MN_SMALL
     assert f.select_path(6144, 7168, 256)[:2] == (f.PATH_MN_LARGE, 1)
+    # K <= 256: the kernel that keeps a tile's partial sums in tensor memory, up to four tiles per SM at K = 256
+    assert f.select_path(1024, 7168, 256) == (f.PATH_MN_LARGE, 1, 256 | f.SHORT_K)
+    assert f.select_path(6144, 7168, 256) == (f.PATH_MN_LARGE, 1, 256)
+    assert f.select_path(6144, 7168, 128) == (f.PATH_MN_LARGE, 1, 256 | f.SHORT_K)
 
 
 def test_dispatch_is_deterministic_and_validates():
@@ -90,6 +94,9 @@ def test_argument_errors_come_back_as_codes_without_touching_a_device():
     assert ex(fake, fake, fake, fake, fake, 128, 128, 256, 0, 128, 1, 2, 0, None, 0, None) == -5    # mn_large cannot split
     assert ex(fake, fake, fake, fake, fake, 128, 128, 256, 0, 128, 0, 0, 192, None, 0, None) == -5  # tile width
     assert ex(fake, fake, fake, fake, fake, 128, 128, 256, 0, 128, 0, 0, 128 | f.TILE_PAIR, None, 0, None) == -5  # pairs are 256 wide
+    assert ex(fake, fake, fake, fake, fake, 128, 128, 384, 0, 128, 0, 0, f.SHORT_K, None, 0, None) == -5        # short K: K <= 256
+    assert ex(fake, fake, fake, fake, fake, 128, 128, 256, 0, 128, 0, 0, 128 | f.SHORT_K, None, 0, None) == -5  # ... 256 wide
+    assert ex(fake, fake, fake, fake, fake, 128, 128, 256, 0, 128, 2, 2, f.SHORT_K, None, 0, None) == -5        # ... K is not cut
     assert ex(fake, fake, fake, fake, fake, 128, 128, 256, 32, 256, 0, 0, 0, None, 0, None) == -5   # n0 % 64
     assert ex(fake, fake, fake, fake, fake, 128, 128, 256, 192, 256, 0, 0, 0, None, 0, None) == -5  # shard beyond n_total
     # forced split-K without a workspace
