@@ -368,6 +368,24 @@ def time_device_kernel(torch, fn, reps=20, warm=3):
     return e0.elapsed_time(e1) * 1e3 / reps
 
 
+def write_only_floor_us(nbytes, reps=20):
+    """Time of a plain write-only kernel (torch fill_, vector stores) over nbytes, rotating over buffers that together
+    exceed the L2: the floor for a launch whose traffic is almost all output.  CUDA events, 3 warm-up launches."""
+    import torch
+    n = max(2, -(-3 * 126 * (1 << 20) // nbytes))
+    bufs = [torch.empty(nbytes // 4, dtype=torch.int32, device="cuda") for _ in range(min(n, 8))]
+    for i in range(3):
+        bufs[i % len(bufs)].fill_(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(reps):
+        bufs[i % len(bufs)].fill_(i)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / reps
+
+
 def format_kernels_bench(torch, f, dev, hbm_gbs):
     """Throughput of the kernels either side of the GEMM (quantize.py:16-67, check.cu:17-22), against the copy
     bandwidth.  Each rotates over three input sets larger than L2 in total."""
@@ -676,11 +694,16 @@ def run_gpu_arm(args, rank, world):
         nl0 = plan_n_shards(shp[1], world)[0][1]
         by = algorithmic_bytes(shp[0], nl0, shp[2], shp[1])
         gbs = by / per_shape_us[i] / 1e3
+        c_bytes = shp[0] * nl0 * 2
+        fill_us = write_only_floor_us(c_bytes)
         roofline_hbm.append({"bound": "hbm", "shape": list(shp), "n_local": nl0, "algorithmic_bytes_per_launch": by,
                              "launch_us": round(per_shape_us[i], 2), "achieved": round(gbs, 1),
                              "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(gbs / peaks["hbm_gbs"], 4),
                              "per": "GPU", "peak_source": "hbm_gbs of %s (copy bandwidth); of %s" % (peak_src, of_what),
-                             "frac_of_nominal_8000": round(gbs / NOMINAL_HBM_GBS, 4)})
+                             "frac_of_nominal_8000": round(gbs / NOMINAL_HBM_GBS, 4),
+                             "output_bytes": c_bytes, "write_only_fill_us": round(fill_us, 2),
+                             "fill_time_over_launch_time": round(fill_us / per_shape_us[i], 4),
+                             "write_only_note": "torch fill_ of the bytes of C alone, same event timing, measured in this run"})
     progress(rank, "CPU baseline")
     cpu = cpu_sweep(CPU_ROWS)
     line = {
