@@ -223,9 +223,9 @@ static int stream_k_ctas(int tiles, int KB, int sm_count)
 
 // Estimated run time of a configuration in microseconds.  The constants come from a measured sweep of
 // every configuration over the 18 benchmark shapes on a B200 (power-capped, cold L2):
-//   per 128-K block of one work unit: 0.44 us (128-wide tile), 0.53 us (256-wide), 0.515 us (256 x 256 pair, with
-//   one multicast commit per barrier: the pair wins from K = 2048 on, 1-3.5 % up to K = 2304, 2-5 % at K = 7168;
-//   at K = 1536 it is 1 % faster at M = 6144 and 3.5 % slower at M = 1024);
+//   per 128-K block of one work unit: 0.44 us (128-wide tile), 0.53 us (256-wide), 0.505 us (256 x 256 pair, with
+//   one multicast commit per K block and the stages freed by a promotion warp: the pair wins from K = 1536 on,
+//   2 % at K = 1536 and M = 6144 (equal at M = 1024), 3-5 % from K = 2048 on; at K = 512 it is 2-8 % slower);
 //   per work unit (tile switch, epilogue): 0.35 / 1.2 / 1.40 us;  per launch: 3.5 us;
 //   split-K through a workspace: 3.5 us + 1 us per split and 128 columns for the partial-sum round trip, doubled
 //   when a CTA has to walk more than one unit (the last-arriver reduction then delays the next unit);
@@ -258,7 +258,7 @@ static double config_cost(const DeviceModel& dm, int M, int N, int K, int tile_n
     const int units = tiles * splits;
     if (dm.sm_count < cg || (mode == 2 && dm.max_clusters[splits] < 1)) return 1e300;   // cannot run on this device
     const int waves = (mode == 2) ? ceil_div(tiles, dm.max_clusters[splits]) : ceil_div(units, dm.sm_count / cg);
-    const double per_kb = (cg == 2) ? 0.515 : (tile_n == 256 ? 0.53 : 0.44);
+    const double per_kb = (cg == 2) ? 0.505 : (tile_n == 256 ? 0.53 : 0.44);
     const double per_unit = (cg == 2) ? 1.40 : (tile_n == 256 ? 1.2 : 0.35);
     double cost = 3.5 + waves * (ceil_div(KB, splits) * per_kb + per_unit);
     if (splits > 1 && mode == 2) {

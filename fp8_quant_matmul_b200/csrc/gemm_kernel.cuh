@@ -40,8 +40,9 @@
 //              byte-wise transposing copy of the reference (mn_large.hip:40-48) has no
 //              counterpart here.
 //   warp 1     MMA issuer.  Per 128-K block: four tcgen05.mma kind::f8f6f4 (K = 32 each) into a
-//              fresh TMEM buffer (the first one overwrites), then commits that publish the TMEM
-//              buffer and free the shared-memory stage.
+//              fresh TMEM buffer (the first one overwrites), then a commit that publishes the TMEM
+//              buffer and, in the three-stage kernels, a second one that frees the shared-memory stage
+//              (with four or more stages a promotion warp frees it, see PROMO_RELEASE).
 //   warp 2     TMA producer for a_scale: boxes of 128 rows x 8 K blocks into a small ring, so the
 //              promotion warps never wait on a global load (mn_large.hip:50-55 stages the
 //              pre-multiplied scales in LDS for the same reason) and pay one barrier round trip
@@ -325,6 +326,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     static_assert(MODE != 2 || CG == 1, "the cluster reduction uses the cluster for the K splits");
     static_assert(MODE != 3 || CG == 1, "stream-K is built for single-CTA tiles");
     constexpr bool RESIDENT = (MODE == 4);              // both K blocks of a tile kept in TMEM (K <= 256)
+    // Who frees a shared-memory stage.  Every tcgen05 instruction costs the issuing thread time, so with four or more
+    // stages the MMA warp issues one commit per K block (TMEM buffer full) and a promotion warp, which learns from that
+    // barrier that the MMAs are done, arrives on the stage's barrier: 1.5-4 % faster on the pair and the 128-wide
+    // kernels.  With three stages (256-wide single-CTA tiles) the later release starves the loads (3-7 % slower),
+    // so there the MMA warp frees the stage with a second commit.
+    constexpr bool PROMO_RELEASE = (STAGES >= 4) && !RESIDENT;
     static_assert(!RESIDENT || (CG == 1 && BN == 256), "the short-K mode uses 256-wide single-CTA tiles");
     // MODE 2: fp32 partial tile of this CTA, rows padded by 16 bytes so that a warp's 32 rows hit distinct banks
     constexpr int PART_PITCH = BN * 4 + 16;
@@ -500,8 +507,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 #ifdef FP8BS_PROFILE
             const long long mma_start = clock64();
 #endif
-            uint32_t peer_base = 0;
-            if constexpr (CG == 2) peer_base = ptx::mapa(bar_base, 1) - bar_base;   // offset to the peer's window
             for (int u = unit0; u < units && ok; u += unit_step) {
                 int tile, m0, n0, kb0, kb1;
                 decode(u, tile, m0, n0, kb0, kb1);
@@ -544,20 +549,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     }
                     // the promotion warps wait on this one; the producer is several stages ahead
                     if constexpr (CG == 2) {
-#ifdef FP8BS_PAIR_PLAIN_COMMITS
-                        ptx::mma_commit_pair(tfull_bar(b) + peer_base);
-                        ptx::mma_commit_pair(tfull_bar(b));
-                        ptx::mma_commit_pair(empty_bar(s));
-                        ptx::mma_commit_pair(empty_bar(s) + peer_base);
-#else
-                        // one commit per barrier reaches both CTAs of the pair (a fourth plain commit per K block costs
-                        // ~100 cycles of tensor-pipe time)
+                        // one commit per barrier reaches both CTAs of the pair (with plain commits, two per barrier, the
+                        // fourth one of a K block cost ~100 cycles of tensor-pipe time)
                         ptx::mma_commit_pair_all(tfull_bar(b), 3);
-                        ptx::mma_commit_pair_all(empty_bar(s), 3);
-#endif
+                        if constexpr (!PROMO_RELEASE) ptx::mma_commit_pair_all(empty_bar(s), 3);
                     } else {
                         if (!RESIDENT || kb == kb1 - 1) ptx::mma_commit(tfull_bar(eb));
-                        ptx::mma_commit(empty_bar(s));
+                        if constexpr (!PROMO_RELEASE) ptx::mma_commit(empty_bar(s));
                     }
                     PROF_TRACE(2, it);
                 }
@@ -752,6 +750,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 PROF_ADD(w_tfull); }
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
+                // the MMAs of this K block are done: its operands' stage may be refilled
+                if constexpr (PROMO_RELEASE)
+                    if (pw == 0 && lane == 0) ptx::mbar_arrive(empty_bar(ait % STAGES));
                 if (pw == 0 && lane == 0) PROF_TRACE(4, ait);
                 if (pw == 1 && lane == 0) PROF_TRACE(7, ait);
                 PROF_T0();

@@ -214,16 +214,10 @@ __device__ __forceinline__ void mma_f8f6f4_pair(uint32_t d_tmem, uint64_t a_desc
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
-// Arrive on `bar` (shared::cluster address, this CTA's or the peer's) once the pair's MMAs issued so far are done.
-__device__ __forceinline__ void mma_commit_pair(uint32_t bar_cluster_addr)
-{
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];"
-                 ::"r"(bar_cluster_addr)
-                 : "memory");
-}
 
-// The same arrival delivered to the barrier at this shared-memory offset in every CTA named in `cta_mask` (bit r = CTA
-// rank r of the cluster): one instruction instead of one commit per CTA.  A commit, not a copy: no data is multicast.
+// Once the pair's MMAs issued so far are done, arrive on the barrier at this shared-memory offset in every CTA named in
+// `cta_mask` (bit r = CTA rank r of the cluster): one instruction instead of one commit per CTA.  A commit, not a copy:
+// no data is multicast.
 __device__ __forceinline__ void mma_commit_pair_all(uint32_t bar, uint16_t cta_mask)
 {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
