@@ -81,20 +81,27 @@ quantize_kernel(const InT* __restrict__ X, uint8_t* __restrict__ out, float* __r
         for (int i = 0; i < 16; ++i) amax[i] = m;      // one scale for the whole 128 x 128 block
     }
     float scale[16];
+    if constexpr (BLOCK_SCALE) {
+        const float a = fmaxf(amax[0], 1e-12f);                       // .clamp(min=1e-12)   quantize.py:29
+        // finfo.max / absmax (quantize.py:30): for a tensor divisor torch evaluates this as reciprocal(absmax) * max
+        const float sc = __fmul_rn(__fdiv_rn(1.0f, a), fp8_max);
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        const float a = fmaxf(amax[i], 1e-12f);                       // .clamp(min=1e-12)   quantize.py:29, 57
-        // finfo.max / absmax (quantize.py:30, 58): for a tensor divisor torch evaluates this as reciprocal(absmax) * max
-        scale[i] = __fmul_rn(__fdiv_rn(1.0f, a), fp8_max);
-    }
-    if constexpr (!BLOCK_SCALE) {
+        for (int i = 0; i < 16; ++i) scale[i] = sc;
+    } else {
+        // Every lane holds all 16 row maxima of its warp.  Lane i works out the scale of row i and its inverse (two exact
+        // divisions instead of 32 per lane) and the scales go round by shuffle.
+        float a = amax[0];
+#pragma unroll
+        for (int i = 1; i < 16; ++i)
+            if ((lane & 15) == i) a = amax[i];
+        a = fmaxf(a, 1e-12f);                                         // .clamp(min=1e-12)   quantize.py:57
+        const float sc = __fmul_rn(__fdiv_rn(1.0f, a), fp8_max);      // reciprocal(absmax) * max, quantize.py:58
+#pragma unroll
+        for (int i = 0; i < 16; ++i) scale[i] = __shfl_sync(0xffffffffu, sc, i);
         // lane i stores the inverse scale of the warp's row i: one 64-byte run per warp
-        float mine = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 16; ++i)
-            if (lane == i) mine = __fdiv_rn(1.0f, scale[i]);                                   // reciprocal, quantize.py:65
         const int rl = warp * 16 + lane;
-        if (lane < 16 && r0 + rl < rows) scale_out[static_cast<size_t>(kb) * rows + r0 + rl] = mine;
+        if (lane < 16 && r0 + rl < rows)
+            scale_out[static_cast<size_t>(kb) * rows + r0 + rl] = __fdiv_rn(1.0f, sc);            // reciprocal, quantize.py:65
     }
     if (BLOCK_SCALE && threadIdx.x == 0)
         scale_out[static_cast<size_t>(kb) * gridDim.x + blockIdx.x] = __fdiv_rn(1.0f, scale[0]);
