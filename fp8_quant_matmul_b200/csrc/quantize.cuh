@@ -9,7 +9,8 @@
 // (out[r + rows*k], the layout of mn_large.hip:13-14) and the inverse scales go to scale_out[r + rows*kb] (row-wise)
 // or scale_out[rb + ceil(rows/128)*kb] (block) -- exactly what the GEMM reads (check.cu:42-46).
 //
-// One CTA handles a 128 x 128 tile: 64 KB read with float4 loads, each thread keeps its 64 values in registers.  The
+// One CTA handles a 128 x 128 tile: 64 KB read with float4 loads, each thread keeps its 64 values in registers (80
+// registers per thread, three CTAs per SM: the scales are applied in place instead of being kept per row).  The
 // fp8 bytes go through shared memory as 32-bit words that hold four consecutive rows at one k -- four bytes that are
 // also neighbours in the column-major output -- laid out [row group][k] with a pitch of 132 words: a thread writes its
 // four k of a row group as one 16-byte store (a warp: 512 contiguous bytes), and reads back 16 bytes with lane = row
@@ -63,62 +64,76 @@ quantize_kernel(const InT* __restrict__ X, uint8_t* __restrict__ out, float* __r
             }
         }
         v[i][0] = x.x; v[i][1] = x.y; v[i][2] = x.z; v[i][3] = x.w;
-        float m = fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w)));
+        amax[i] = fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w)));   // this lane's 4 k of row i
+    }
+    // Row maxima over the 32 lanes by a halving butterfly: at offset 16 a lane keeps 8 of its 16 rows and hands the other
+    // 8 to its partner, at offset 8 it keeps 4, ... : 8 + 4 + 2 + 1 + 1 = 16 shuffles instead of 5 per row (80).
+    // Afterwards lanes 2r and 2r + 1 both hold the absmax of the warp's row r over the 128 k.
+    float rowmax;
+    {
+        const bool b4 = (lane & 16) != 0, b3 = (lane & 8) != 0, b2 = (lane & 4) != 0, b1 = (lane & 2) != 0;
+        float h8[8], h4[4], h2[2];
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-        amax[i] = m;                                   // every lane: absmax of row i over the 128 k
+        for (int j = 0; j < 8; ++j) {
+            const float give = b4 ? amax[j] : amax[j + 8], keep = b4 ? amax[j + 8] : amax[j];
+            h8[j] = fmaxf(keep, __shfl_xor_sync(0xffffffffu, give, 16));
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float give = b3 ? h8[j] : h8[j + 4], keep = b3 ? h8[j + 4] : h8[j];
+            h4[j] = fmaxf(keep, __shfl_xor_sync(0xffffffffu, give, 8));
+        }
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const float give = b2 ? h4[j] : h4[j + 2], keep = b2 ? h4[j + 2] : h4[j];
+            h2[j] = fmaxf(keep, __shfl_xor_sync(0xffffffffu, give, 4));
+        }
+        const float give = b1 ? h2[0] : h2[1], keep = b1 ? h2[1] : h2[0];
+        rowmax = fmaxf(keep, __shfl_xor_sync(0xffffffffu, give, 2));
+        rowmax = fmaxf(rowmax, __shfl_xor_sync(0xffffffffu, rowmax, 1));       // row (lane >> 1) & 15
     }
     if constexpr (BLOCK_SCALE) {
-        float m = 0.f;
+        float m = rowmax;                              // max over the warp's 16 rows: lanes 0, 2, .., 30 hold them
 #pragma unroll
-        for (int i = 0; i < 16; ++i) m = fmaxf(m, amax[i]);
+        for (int o = 16; o > 1; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
         if (lane == 0) warp_max[warp] = m;
         __syncthreads();
         m = warp_max[0];
 #pragma unroll
         for (int w = 1; w < 8; ++w) m = fmaxf(m, warp_max[w]);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) amax[i] = m;      // one scale for the whole 128 x 128 block
+        rowmax = m;                                    // one scale for the whole 128 x 128 block
     }
-    float scale[16];
+    // The scale of a row (or of the block) is applied in place, so that no per-row scale stays live in the loops below.
+    float sc;
     if constexpr (BLOCK_SCALE) {
-        const float a = fmaxf(amax[0], 1e-12f);                       // .clamp(min=1e-12)   quantize.py:29
+        const float a = fmaxf(rowmax, 1e-12f);                        // .clamp(min=1e-12)   quantize.py:29
         // finfo.max / absmax (quantize.py:30): for a tensor divisor torch evaluates this as reciprocal(absmax) * max
-        const float sc = __fmul_rn(__fdiv_rn(1.0f, a), fp8_max);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) scale[i] = sc;
+        sc = __fmul_rn(__fdiv_rn(1.0f, a), fp8_max);
+        if (threadIdx.x == 0) scale_out[static_cast<size_t>(kb) * gridDim.x + blockIdx.x] = __fdiv_rn(1.0f, sc);
     } else {
-        // Every lane holds all 16 row maxima of its warp.  Lane i works out the scale of row i and its inverse (two exact
-        // divisions instead of 32 per lane) and the scales go round by shuffle.
-        float a = amax[0];
-#pragma unroll
-        for (int i = 1; i < 16; ++i)
-            if ((lane & 15) == i) a = amax[i];
-        a = fmaxf(a, 1e-12f);                                         // .clamp(min=1e-12)   quantize.py:57
-        const float sc = __fmul_rn(__fdiv_rn(1.0f, a), fp8_max);      // reciprocal(absmax) * max, quantize.py:58
-#pragma unroll
-        for (int i = 0; i < 16; ++i) scale[i] = __shfl_sync(0xffffffffu, sc, i);
-        // lane i stores the inverse scale of the warp's row i: one 64-byte run per warp
-        const int rl = warp * 16 + lane;
-        if (lane < 16 && r0 + rl < rows)
+        // lanes 2r and 2r + 1 work out the scale of the warp's row r and its inverse (two exact divisions per lane);
+        // the scales go round by shuffle below
+        const float a = fmaxf(rowmax, 1e-12f);                        // .clamp(min=1e-12)   quantize.py:57
+        sc = __fmul_rn(__fdiv_rn(1.0f, a), fp8_max);                  // reciprocal(absmax) * max, quantize.py:58
+        // the even lanes store the inverse scales of the warp's 16 rows: one 64-byte run per warp
+        const int rl = warp * 16 + (lane >> 1);
+        if ((lane & 1) == 0 && r0 + rl < rows)
             scale_out[static_cast<size_t>(kb) * rows + r0 + rl] = __fdiv_rn(1.0f, sc);            // reciprocal, quantize.py:65
     }
-    if (BLOCK_SCALE && threadIdx.x == 0)
-        scale_out[static_cast<size_t>(kb) * gridDim.x + blockIdx.x] = __fdiv_rn(1.0f, scale[0]);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const float s_i = BLOCK_SCALE ? sc : __shfl_sync(0xffffffffu, sc, 2 * i);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            v[i][j] = fminf(fmaxf(__fmul_rn(v[i][j], s_i), -fp8_max), fp8_max);    // .clamp(min, max)    quantize.py:33, 61
+    }
     // quantise; rows 4g .. 4g+3 of this warp at k = 4*lane + j become one word
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
         uint32_t w[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            float q[4];
-#pragma unroll
-            for (int t = 0; t < 4; ++t) {
-                const float x = __fmul_rn(v[4 * g + t][j], scale[4 * g + t]);
-                q[t] = fminf(fmaxf(x, -fp8_max), fp8_max);             // .clamp(min, max)    quantize.py:33, 61
-            }
-            w[j] = cvt_e4m3x2(q[0], q[1]) | (cvt_e4m3x2(q[2], q[3]) << 16);
-        }
+        for (int j = 0; j < 4; ++j)
+            w[j] = cvt_e4m3x2(v[4 * g][j], v[4 * g + 1][j]) | (cvt_e4m3x2(v[4 * g + 2][j], v[4 * g + 3][j]) << 16);
         *reinterpret_cast<uint4*>(&tile[(warp * 4 + g) * PITCH + lane * 4]) = make_uint4(w[0], w[1], w[2], w[3]);
     }
     __syncthreads();
