@@ -1120,17 +1120,28 @@ __device__ __forceinline__ uint32_t fnuz_to_fn_byte(uint32_t b, unsigned int& in
     return sign | h;                                    // h <= 8; 8 is the encoding of 2^-6
 }
 
-// Four bytes at a time.  A byte whose low seven bits are >= 0x10 (exponent field >= 2) is a normal number of both
-// dialects and only loses 8; a word of four such bytes -- nearly every word of real data -- is one subtraction.
+// Four bytes at a time, without a branch on the data (in real data one word in twenty holds a small magnitude, so a
+// branch would send nearly every warp down the slow path).  Per byte, with low7 = b & 0x7F:
+//   low7 >= 0x10 (exponent field >= 2): a normal number of both dialects, the byte only loses 8;
+//   low7 <  0x10: the value is low7 * 2^-10, i.e. (low7 / 2) * 2^-9 rounded half to even, counted when low7 is odd;
+//   0x80 (the NaN of e4m3fnuz) becomes 0x7F.
 __device__ __forceinline__ uint32_t fnuz_to_fn_word(uint32_t w, unsigned int& inexact)
 {
-    const uint32_t low7 = w & 0x7F7F7F7Fu;
-    // per byte: bit 7 set iff low7 >= 0x10  (adding 0x70 carries into bit 7 exactly then; no carry crosses bytes)
-    if (((low7 + 0x70707070u) & 0x80808080u) == 0x80808080u) return w - 0x08080808u;
-    uint32_t o = 0;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) o |= fnuz_to_fn_byte((w >> (8 * j)) & 0xFFu, inexact) << (8 * j);
-    return o;
+    const uint32_t low7 = w & 0x7F7F7F7Fu, sign = w & 0x80808080u;
+    const uint32_t big = (low7 + 0x70707070u) & 0x80808080u;            // 0x80 in every byte with low7 >= 0x10
+    if (big == 0x80808080u) return w - 0x08080808u;                      // warp-uniform for most words of real data
+    const uint32_t big_ff = (big >> 7) * 0xFFu;                          // ... as a byte mask
+    // setting bit 7 first keeps the borrow of a small byte out of its neighbour
+    const uint32_t cand_big = (((low7 | 0x80808080u) - 0x08080808u) & 0x7F7F7F7Fu) | sign;
+    uint32_t h = (low7 >> 1) & 0x7F7F7F7Fu;                             // per byte: low7 / 2
+    const uint32_t odd = low7 & 0x01010101u;
+    h += odd & h;                                                        // tie: round half to even (h <= 7, no carry)
+    const uint32_t cand_small = sign | h;
+    inexact += __popc(odd & ~(big >> 7));
+    uint32_t r = (cand_big & big_ff) | (cand_small & ~big_ff);
+    const uint32_t zero7 = ~(low7 + 0x7F7F7F7Fu) & 0x80808080u;         // 0x80 in every byte with low7 == 0
+    const uint32_t nan_ff = ((zero7 & sign) >> 7) * 0xFFu;              // bytes equal to 0x80
+    return (r & ~nan_ff) | (0x7F7F7F7Fu & nan_ff);
 }
 
 __global__ void __launch_bounds__(256)
