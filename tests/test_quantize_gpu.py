@@ -113,3 +113,34 @@ def test_fnuz_bytes_from_the_reference_format_are_ingested_on_the_device():
             n_bad += 1
             assert abs(have - want) <= 2.0 ** -10                        # rounded to the neighbouring multiple of 2^-9
     assert n_bad == inexact and inexact > 0
+
+
+def test_fnuz_words_mix_small_and_normal_bytes_in_every_position():
+    # The device kernel works on 32-bit words with byte-parallel arithmetic: every pair of byte values side by side, at both
+    # word alignments, must come out as the per-byte table says (a borrow or a carry must never reach the neighbouring byte)
+    dev = torch.device("cuda:0")
+    L = h.oracle_lib()
+    fn_of_value = {}
+    for g in range(256):
+        v = L.oracle_e4m3fn_to_float(g)
+        if v == v and not (g == 0x80):                                   # skip NaN and -0
+            fn_of_value.setdefault(v, g)
+    table = np.zeros(256, np.uint8)
+    odd = np.zeros(256, np.int64)
+    for b in range(256):
+        v = L.oracle_e4m3fnuz_to_float(b)
+        if v != v:
+            table[b] = 0x7F
+            continue
+        if v not in fn_of_value:                                         # an odd multiple of 2^-10 below 2^-6
+            odd[b] = 1
+            v = round(v * 512.0) / 512.0                                 # Python rounds half to even
+        table[b] = fn_of_value[v] if v != 0 else (b & 0x80)              # -2^-10 rounds to -0, which keeps its sign
+    assert odd.sum() == 16                                               # eight magnitudes, two signs
+    b0, b1 = np.meshgrid(np.arange(256, dtype=np.uint8), np.arange(256, dtype=np.uint8), indexing="ij")
+    pairs = np.stack([b0.ravel(), b1.ravel()], axis=1).ravel()           # 131072 bytes
+    for lead in (0, 1, 2, 3):
+        buf = np.concatenate([np.full(lead, 0x38, np.uint8), pairs, np.full(5, 0x0B, np.uint8)])
+        d, inexact = f.fnuz_to_fn_device(torch.from_numpy(buf).to(dev))
+        assert np.array_equal(d.cpu().numpy(), table[buf]), "lead %d" % lead
+        assert inexact == int(odd[buf].sum())
