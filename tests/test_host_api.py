@@ -216,3 +216,26 @@ def test_dispatch_for_a_smaller_gpu_never_needs_more_resident_ctas_than_sms():
         assert f.select_path_sms(M, N, K, 148)[:3] == f.select_path(M, N, K)
     with pytest.raises(f.Fp8bsError):
         f.select_path_sms(1024, 512, 7168, 0)
+
+
+def test_short_k_dispatch_rule():
+    # K = 128: always the kernel that keeps a tile's partial sums in tensor memory; K = 256: up to four 128 x 256 tiles per SM
+    for (M, N) in ((128, 64), (1024, 7168), (6144, 7168), (16384, 7168)):
+        path, splits, tile_n = f.select_path(M, N, 128)
+        assert (path, splits, tile_n) == (f.PATH_MN_LARGE, 1, 256 | f.SHORT_K)
+    sms = 148
+    for (M, N) in ((1024, 7168), (2048, 7168), (2048, 9472), (6144, 7168), (6144, 3584), (6144, 1792)):
+        tiles = -(-M // 128) * -(-N // 256)
+        path, splits, tile_n = f.select_path(M, N, 256)
+        assert path == f.PATH_MN_LARGE and splits == 1
+        assert bool(tile_n & f.SHORT_K) == (tiles <= 4 * sms), (M, N, tiles, hex(tile_n))
+        assert f.workspace_bytes(M, N, 256) == 0
+    # the rule follows the SM count it is asked about
+    p, s_, t, _ = f.select_path_sms(6144, 7168, 256, 148)
+    assert not (t & f.SHORT_K)
+    p, s_, t, _ = f.select_path_sms(1024, 7168, 256, 36)
+    assert not (t & f.SHORT_K)                                          # 448 tiles on 36 SMs: more than four per SM
+    # longer K never takes it
+    for K in (384, 512, 7168):
+        assert not (f.select_path(1024, 7168, K)[2] & f.SHORT_K)
+    assert f.workspace_bytes(1024, 7168, 256, f.PATH_MN_LARGE, 1, f.SHORT_K) == 0
