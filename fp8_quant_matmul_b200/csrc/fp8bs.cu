@@ -239,7 +239,7 @@ static int stream_k_ctas(int tiles, int KB, int sm_count)
 // is why the estimate keeps stream-K for shapes with very few, very long tiles only.
 constexpr double STREAM_K_FIXUP_US = 6.0;
 // Mode 4 (K <= 256, partial sums resident in TMEM) is chosen by rule, see choose_config.
-constexpr int SHORT_K_MAX_WAVES = 4;
+constexpr int SHORT_K_MAX_WAVES = 3;
 static double config_cost(const DeviceModel& dm, int M, int N, int K, int tile_n, int splits, int cg, int mode)
 {
     const int KB = K / 128;
@@ -288,10 +288,11 @@ static Config choose_config(const DeviceModel& dm, int M, int N, int K, int path
     // short K: the tile's partial sums stay in TMEM (mode 4), a member of the mn_large family (K is not cut)
     if (tile_n & FP8BS_SHORT_K) return Config{FP8BS_PATH_MN_LARGE, 256, 1, 1, 4, 0};
     if (KB <= 2 && path != FP8BS_PATH_MN_SMALL && splits <= 1 && !force_ws && !force_sk && want_tile == 0) {
-        // Measured on a B200: 5-6 % faster than the full-K kernel at K = 128 and, at K = 256, up to about four tiles
-        // per SM (1024 x 7168 x 256: 7.20 against 7.64 us); with more tiles both kernels write C as fast as the
-        // memory takes it and the full-K kernel, which overlaps the MMAs of a tile with the scaling of the one
-        // before, is 3 % ahead (6144 x 7168 x 256: 23.7 against 24.4 us).
+        // Measured on a B200: 5-6 % faster than the full-K kernel at K = 128 and, at K = 256, up to about three tiles
+        // per SM (1024 x 7168 x 256, 1.5 per SM: 7.20 against 7.64 us; 2048 x 7168 x 256, 3.0: 11.1 against 11.4);
+        // with more tiles the store path of the SMs sets the pace and the full-K kernel, which overlaps the MMAs of
+        // a tile with the scaling of the one before, is ahead (3072 x 7168 x 256, 4.5 per SM: 14.1 against 14.9 us;
+        // 6144 x 7168 x 256, 9.1: 23.7 against 24.4).
         const int tiles = ceil_div(M, 128) * ceil_div(N, 256);
         if (KB == 1 || tiles <= SHORT_K_MAX_WAVES * dm.sm_count) return Config{FP8BS_PATH_MN_LARGE, 256, 1, 1, 4, 0};
     }

@@ -55,7 +55,7 @@ def test_dispatch_policy_on_the_18_shapes():
     assert f.select_path(1024, 512, 7168)[0] == f.PATH_MN_SMALL
     assert f.select_path(1024, 576, 7168)[0] == f.PATH_MN_SMALL
     assert f.select_path(6144, 7168, 256)[:2] == (f.PATH_MN_LARGE, 1)
-    # K <= 256: the kernel that keeps a tile's partial sums in tensor memory, up to four tiles per SM at K = 256
+    # K <= 256: the kernel that keeps a tile's partial sums in tensor memory, up to three tiles per SM at K = 256
     assert f.select_path(1024, 7168, 256) == (f.PATH_MN_LARGE, 1, 256 | f.SHORT_K)
     assert f.select_path(6144, 7168, 256) == (f.PATH_MN_LARGE, 1, 256)
     assert f.select_path(6144, 7168, 128) == (f.PATH_MN_LARGE, 1, 256 | f.SHORT_K)
@@ -219,22 +219,22 @@ def test_dispatch_for_a_smaller_gpu_never_needs_more_resident_ctas_than_sms():
 
 
 def test_short_k_dispatch_rule():
-    # K = 128: always the kernel that keeps a tile's partial sums in tensor memory; K = 256: up to four 128 x 256 tiles per SM
+    # K = 128: always the kernel that keeps a tile's partial sums in tensor memory; K = 256: up to three 128 x 256 tiles per SM
     for (M, N) in ((128, 64), (1024, 7168), (6144, 7168), (16384, 7168)):
         path, splits, tile_n = f.select_path(M, N, 128)
         assert (path, splits, tile_n) == (f.PATH_MN_LARGE, 1, 256 | f.SHORT_K)
     sms = 148
-    for (M, N) in ((1024, 7168), (2048, 7168), (2048, 9472), (6144, 7168), (6144, 3584), (6144, 1792)):
+    for (M, N) in ((1024, 7168), (2048, 7168), (1536, 9472), (6144, 7168), (6144, 3584), (6144, 1792)):
         tiles = -(-M // 128) * -(-N // 256)
         path, splits, tile_n = f.select_path(M, N, 256)
         assert path == f.PATH_MN_LARGE and splits == 1
-        assert bool(tile_n & f.SHORT_K) == (tiles <= 4 * sms), (M, N, tiles, hex(tile_n))
+        assert bool(tile_n & f.SHORT_K) == (tiles <= 3 * sms), (M, N, tiles, hex(tile_n))
         assert f.workspace_bytes(M, N, 256) == 0
     # the rule follows the SM count it is asked about
     p, s_, t, _ = f.select_path_sms(6144, 7168, 256, 148)
     assert not (t & f.SHORT_K)
     p, s_, t, _ = f.select_path_sms(1024, 7168, 256, 36)
-    assert not (t & f.SHORT_K)                                          # 448 tiles on 36 SMs: more than four per SM
+    assert not (t & f.SHORT_K)                                          # 224 tiles on 36 SMs: more than three per SM
     # longer K never takes it
     for K in (384, 512, 7168):
         assert not (f.select_path(1024, 7168, K)[2] & f.SHORT_K)
